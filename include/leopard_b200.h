@@ -649,6 +649,8 @@ typedef struct lp_latent_desc {
   float* cache; int page_size;
   const int* page_table; int max_pages;
   int window; float scale;
+  const float* sink;                        /* [heads] or NULL: exp(sink[h]) joins head h's softmax denominator (no key, no value, not scaled) */
+  const float* gate; long long ldg;         /* [rows, ldg] or NULL: head h's output is multiplied by sigmoid(gate[r, h]) */
 } lp_latent_desc;
 int lp_latent_prep(const lp_latent_desc* desc, int R, const int* row_seq, const int* row_pos, void* stream);
 /* q_abs fp32 [rows, heads * kv_rank] = per-head W_uk^T q_unrotated; out [rows, heads * kv_rank] = softmax-weighted sum of cached c */
@@ -665,7 +667,7 @@ int lp_latent_attend(const lp_latent_desc* desc, int R, const int* row_seq, cons
  * score = q . k * scale, then softcap * tanh(score / softcap) when softcap > 0.  One softmax over everything visible; sink != 0 adds
  * 1 to its denominator (a key of score 0 without a value).  Query head h reads key / value head h / (heads / kv_heads).
  * norm_mode: RMS norm of q and k before rotation — LP_QKNORM_NONE, LP_QKNORM_HEAD (over each head's dim, gains [dim] shared by the
- * heads) or LP_QKNORM_FULL (over the whole projection, gains [heads * dim] and [kv_heads * dim]).  q and k are rotated on the first
+ * heads) or LP_QKNORM_FULL (over the whole projection, gains [heads * dim] and [kv_heads * dim]); both gains NULL: a norm without gains.  q and k are rotated on the first
  * rot_dims dimensions of a head; with v_inv_freq the values are rotated over v_rot_dims (cached so) and every head's output is
  * turned back by its query's position. */
 enum lp_qknorm_mode { LP_QKNORM_NONE = 0, LP_QKNORM_HEAD = 1, LP_QKNORM_FULL = 2 };
@@ -679,6 +681,10 @@ typedef struct lp_window_attn_desc {
   float* pooled; const int* pooled_table; int max_pooled_pages; int pool;
   int window; int keep_first;
   float scale, softcap; int sink;
+  const float* q_bias; const float* k_bias; const float* v_bias;   /* biases of the projections (NULL: none), added by lp_window_attn_prep */
+  int v_norm;                               /* != 0: every value head is divided by its root mean square (eps) and cached so */
+  const float* talk;                        /* [heads, heads] fp32 or NULL: softmax weights mixed over the heads (lp_window_attn_talk) */
+  int g_off;                                /* >= 0: column of an output gate in qkv, heads * vdim wide; out *= sigmoid(g) (lp_window_attn_talk) */
 } lp_window_attn_desc;
 /* norm + rotation of the step's rows; keys and values go to the request's pages */
 int lp_window_attn_prep(const lp_window_attn_desc* desc, int R, const int* row_seq, const int* row_pos, void* stream);
@@ -689,6 +695,10 @@ int lp_window_attn_pool(const lp_window_attn_desc* desc, int n_seqs, const int* 
 /* out [rows, heads * vdim] fp32 or bf16 */
 int lp_window_attn(const lp_window_attn_desc* desc, int R, const int* row_seq, const int* row_pos, void* out, long long ldo,
                    int out_fp32, void* stream);
+/* talking heads: weight_h(i, j) <- sum_g talk[h, g] weight_g(i, j) after the softmax of every head, head h applying its mixed weights to
+ * the values of its own key / value head; every visibility rule, the cap and the sink as above; the gate of g_off when it is given */
+int lp_window_attn_talk(const lp_window_attn_desc* desc, int R, const int* row_seq, const int* row_pos, void* out, long long ldo,
+                        int out_fp32, void* stream);
 /* the same result for the rows of prompts, computed per tile of consecutive rows of one request: the chunk tables of
  * lp_retention_prefill (at most LP_RETENTION_CHUNK rows a chunk, never across requests) say which rows belong together */
 int lp_window_attn_tiles(const lp_window_attn_desc* desc, int R, const int* row_seq, const int* row_pos, int n_chunks, const int* chunk_seq,
@@ -711,12 +721,46 @@ int lp_mingru_prefill(const lp_mingru_desc* desc, int n_seqs, int n_chunks, cons
                       size_t workspace_bytes, void* stream);
 int lp_mingru_decode(const lp_mingru_desc* desc, int n_seqs, const int* seq_row0, const int* seq_pos0, const int* seq_slot, void* stream);
 
+/* mLSTM (csrc/lp_mlstm.cu): per head a matrix memory S [dim, vdim], a normaliser n [dim] and a running maximum m (starts at 0).
+ * proj fp32 [rows, ld] holds q | k (heads x dim), v | g (heads x vdim) and the two gate pre-activations (heads each) at the given column
+ * offsets.  i = cap tanh((a_i + i_bias) / cap), f = logsigmoid(cap tanh((a_f + f_bias) / cap)), m_t = max(f + m_(t-1), i),
+ * S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T, n_t likewise with k alone, o = S_t^T (q_scale q) / (max(|n_t . q_scale q|,
+ * exp(-m_t)) + 1e-6); out = o / rms(o) per head (eps) * out_gain (NULL: none) * sigmoid(g).  state fp32 [slots][heads][dim + 1][vdim + 1]
+ * (slot_stride elements per slot), carried between steps; a request at position 0 starts from zero without reading its slot.
+ * Request s owns rows [seq_row0[s], seq_row0[s+1]) from position seq_pos0[s]; one-token steps and prompts take the same call. */
+typedef struct lp_mlstm_desc {
+  const float* proj; long long ld; int q_off, k_off, v_off, g_off, i_off, f_off;
+  int heads, dim, vdim;
+  const float* i_bias; const float* f_bias;   /* [heads] */
+  float gate_cap, q_scale, eps;
+  const float* out_gain;                      /* [heads * vdim] */
+  float* state; long long slot_stride;
+  void* out; long long ldo; int out_fp32;
+} lp_mlstm_desc;
+size_t lp_mlstm_workspace_bytes(int rows, int heads, int vdim);
+int lp_mlstm(const lp_mlstm_desc* desc, int n_seqs, int R, const int* seq_row0, const int* seq_pos0, const int* seq_slot, void* workspace,
+             size_t workspace_bytes, void* stream);
+
+/* x[r, 2i] += sin(row_pos[r] * freq[i]), x[r, 2i + 1] += cos(...): absolute sinusoidal positions; freq fp32 [ceil(D / 2)] */
+int lp_add_positions_f32(float* x, long long ldx, int R, int D, const int* row_pos, const float* freq, void* stream);
+/* x[r, :] += v for every row */
+int lp_add_row_f32(float* x, long long ldx, const float* v, int M, int N, void* stream);
+/* token shift: out[r] = h[r] + (h[r - 1] - h[r]) * mu per channel; the row before a request's first row of the step is the request's
+ * slot of `state` (zeros at position 0), which afterwards holds the request's last row.  Not in place. */
+int lp_token_shift_f32(const float* h, long long ldh, const float* mu, int R, int D, const int* row_seq, const int* row_pos,
+                       const int* seq_row0, const int* seq_slot, float* state, long long slot_stride, void* out, long long ldo,
+                       int out_fp32, void* stream);
+
 /* y <- y + alpha * x over fp32 [M, N] (the residual update after a product that ran on the tensor cores) */
 int lp_axpy_f32(float* y, long long ldy, const float* x, long long ldx, float alpha, int M, int N, void* stream);
 
 int lp_moe_route(const void* h, long long ldh, int h_fp32, int T, int D, const void* w_router, long long ldw, int E,
                  const float* correction, int n_groups, int keep_groups, int top, const void* w_gate, int* idx_out, float* w_out,
                  float* gate_out, void* stream);
+/* the plain token-choice router: logits = W_router h + logit_bias (NULL: none), the `top` largest are chosen (ties to the lower index),
+ * weights = softmax over the chosen logits only */
+int lp_moe_route_softmax(const void* h, long long ldh, int h_fp32, int T, int D, const void* w_router, long long ldw, int E,
+                         const float* logit_bias, int top, int* idx_out, float* w_out, void* stream);
 int lp_moe_max_tiles(int n_pairs, int E, int tile_rows);
 int lp_moe_align(const int* idx, int n_pairs, int top, int E, int tile_rows, int max_tiles, int* tile_group, int* sorted_token,
                  int* pair_row, void* stream);

@@ -96,7 +96,8 @@ class WindowAttnDesc(C.Structure):
                 ("vdim", _i), ("norm_mode", _i), ("q_gain", _vp), ("k_gain", _vp), ("eps", _f), ("inv_freq", _vp), ("rot_dims", _i),
                 ("rot_layout", _i), ("rot_mscale", _f), ("v_inv_freq", _vp), ("v_rot_dims", _i), ("v_rot_layout", _i), ("cache", _vp),
                 ("page_size", _i), ("page_table", _vp), ("max_pages", _i), ("pooled", _vp), ("pooled_table", _vp),
-                ("max_pooled_pages", _i), ("pool", _i), ("window", _i), ("keep_first", _i), ("scale", _f), ("softcap", _f), ("sink", _i)]
+                ("max_pooled_pages", _i), ("pool", _i), ("window", _i), ("keep_first", _i), ("scale", _f), ("softcap", _f), ("sink", _i),
+                ("q_bias", _vp), ("k_bias", _vp), ("v_bias", _vp), ("v_norm", _i), ("talk", _vp), ("g_off", _i)]
 
 
 class MinGRUDesc(C.Structure):
@@ -116,7 +117,15 @@ class LatentDesc(C.Structure):
     """lp_latent_desc (include/leopard_b200.h)."""
     _fields_ = [("q", _vp), ("ldq", _ll), ("dkv", _vp), ("lddkv", _ll), ("heads", _i), ("dim", _i), ("rot_dim", _i), ("kv_rank", _i),
                 ("c_gain", _vp), ("eps", _f), ("inv_freq", _vp), ("rot_dims", _i), ("rot_layout", _i), ("rot_mscale", _f),
-                ("cache", _vp), ("page_size", _i), ("page_table", _vp), ("max_pages", _i), ("window", _i), ("scale", _f)]
+                ("cache", _vp), ("page_size", _i), ("page_table", _vp), ("max_pages", _i), ("window", _i), ("scale", _f),
+                ("sink", _vp), ("gate", _vp), ("ldg", _ll)]
+
+
+class MLSTMDesc(C.Structure):
+    """lp_mlstm_desc (include/leopard_b200.h)."""
+    _fields_ = [("proj", _vp), ("ld", _ll), ("q_off", _i), ("k_off", _i), ("v_off", _i), ("g_off", _i), ("i_off", _i), ("f_off", _i),
+                ("heads", _i), ("dim", _i), ("vdim", _i), ("i_bias", _vp), ("f_bias", _vp), ("gate_cap", _f), ("q_scale", _f),
+                ("eps", _f), ("out_gain", _vp), ("state", _vp), ("slot_stride", _ll), ("out", _vp), ("ldo", _ll), ("out_fp32", _i)]
 
 
 # name -> (restype, argtypes); must list EVERY symbol include/leopard_b200.h declares (tests/test_abi.py checks)
@@ -214,6 +223,13 @@ _SIGS = {
     "lp_window_attn_pool": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _i, _vp]),
     "lp_window_attn": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _vp, _ll, _i, _vp]),
     "lp_window_attn_tiles": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _i, _vp]),
+    "lp_window_attn_talk": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _vp, _ll, _i, _vp]),
+    "lp_mlstm_workspace_bytes": (_sz, [_i, _i, _i]),
+    "lp_mlstm": (_i, [C.POINTER(MLSTMDesc), _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "lp_add_positions_f32": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp]),
+    "lp_add_row_f32": (_i, [_vp, _ll, _vp, _i, _i, _vp]),
+    "lp_token_shift_f32": (_i, [_vp, _ll, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _vp]),
+    "lp_moe_route_softmax": (_i, [_vp, _ll, _i, _i, _i, _vp, _ll, _i, _vp, _i, _vp, _vp, _vp]),
     "lp_mingru_workspace_bytes": (_sz, [_i, _i]),
     "lp_mingru_prefill": (_i, [C.POINTER(MinGRUDesc), _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "lp_mingru_decode": (_i, [C.POINTER(MinGRUDesc), _i, _vp, _vp, _vp, _vp]),
@@ -265,7 +281,7 @@ def lib():
     return _lib
 
 
-# ---- the 32-bit residual-stream entry points (csrc/lp_linear.cu, lp_stream32.cu, lp_seqmix.cu, lp_winattn.cu, lp_mingru.cu, lp_moe.cu) -----------------------------------
+# ---- the 32-bit residual-stream entry points (csrc/lp_linear.cu, lp_stream32.cu, lp_seqmix.cu, lp_winattn.cu, lp_mingru.cu, lp_mlstm.cu, lp_moe.cu) -----------------------------------
 # They need none of the tcgen05 translation units, so a model that uses only them can run from a library of its own that compiles in
 # seconds (build.build_native("stream32")); the full library contains the same symbols and is preferred when it is already built.
 STREAM32_LIB_PATH = PKG / "lib" / "libleopard_stream32.so"
@@ -274,7 +290,8 @@ STREAM32_SYMBOLS = ("lp_last_error", "lp_abi_version", "lp_launch_count", "lp_li
                     "lp_retention_decode", "lp_latent_prep", "lp_latent_attend", "lp_moe_route", "lp_moe_max_tiles", "lp_moe_align",
                     "lp_moe_combine", "lp_axpy_f32", "lp_window_attn_prep", "lp_window_attn_pool", "lp_window_attn", "lp_window_attn_tiles",
                     "lp_mingru_workspace_bytes",
-                    "lp_mingru_prefill", "lp_mingru_decode")
+                    "lp_mingru_prefill", "lp_mingru_decode", "lp_window_attn_talk", "lp_mlstm_workspace_bytes", "lp_mlstm",
+                    "lp_add_positions_f32", "lp_add_row_f32", "lp_token_shift_f32", "lp_moe_route_softmax")
 STREAM32_OPTIONAL = ("lp_gemm_bf16",)      # present in the native libraries, absent from the CPU-emulated build
 _stream32 = None
 

@@ -45,7 +45,7 @@ def _digest(paths) -> str:
 # components: a library of its own for a subset of the sources (the full library contains every component)
 COMPONENTS = {
     # decoder-only language models on the 32-bit residual-stream kernels, plus the tcgen05 GEMM that takes their large bf16 products
-    "stream32": ("lp_host.cu", "lp_linear.cu", "lp_stream32.cu", "lp_seqmix.cu", "lp_winattn.cu", "lp_mingru.cu", "lp_moe.cu", "lp_gemm.cu",
+    "stream32": ("lp_host.cu", "lp_linear.cu", "lp_stream32.cu", "lp_seqmix.cu", "lp_winattn.cu", "lp_mingru.cu", "lp_mlstm.cu", "lp_moe.cu", "lp_gemm.cu",
                  "lp_gemm4.cu"),
 }
 

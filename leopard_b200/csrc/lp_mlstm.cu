@@ -1,0 +1,233 @@
+// leopard_b200 — mLSTM: a matrix memory per head with exponential gates and a running stabiliser, everything after the projections
+// in 32-bit floats.
+//
+// Per head, with q (scaled by q_scale), k [dim], v [vdim] and two gate pre-activations a_i, a_f of the token:
+//   i = cap * tanh((a_i + b_i) / cap)                       log input gate
+//   f = logsigmoid(cap * tanh((a_f + b_f) / cap))           log forget gate
+//   m_t = max(f + m_(t-1), i),  m_(-1) = 0                  running maximum (starts at 0, not at minus infinity)
+//   S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T        S [dim, vdim], starts at zero
+//   n_t = the same recurrence with k alone                            n [dim]
+//   o_t = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6)
+// then o / rms(o) per head (eps), times a gain per channel, times sigmoid(g).
+//
+//   lp_mlstm   two kernels for prompts, portions and one-token steps alike:
+//     scan     a CTA per (request, head, tile of 32 state columns); the normaliser n is one more COLUMN of the state (its "value" is
+//              1), so S and n share the code.  A thread owns 32 rows of one column in registers (threadIdx.y picks the rows when dim
+//              exceeds 32).  Tokens are staged in shared memory 16 at a time: the gate transforms of the 16 tokens in parallel, the
+//              running maximum by one thread (two adds and a max per token), the two exponentials per token in parallel, then the
+//              16 state updates without any synchronisation; the partial read-outs of the row groups meet in shared memory once per
+//              16 tokens.  The state is read from and written to the request's slot ([dim + 1][vdim + 1] per head: S | n, and m
+//              in the last row, one copy per column tile) — a request at position 0 starts from zero without reading it.
+//     finish   a warp per (row, head): denominator, unit RMS, gain, gate.
+// The recurrence is run token by token in every case, so a row's result does not depend on how the tokens were cut into steps.
+#include "lp_host.h"
+#include "../../include/leopard_b200.h"
+
+namespace lp {
+
+typedef __nv_bfloat16 bf16;
+
+struct MlstmArgs {
+  const float* proj; long long ld; int q_off, k_off, v_off, g_off, i_off, f_off;
+  int heads, dim, vdim;
+  const float* i_bias; const float* f_bias;
+  float gate_cap, q_scale, eps;
+  const float* out_gain;
+  float* state; long long slot_stride;
+  void* out; long long ldo; int out_fp32;
+};
+
+constexpr int MLSTM_COLS = 32;      // state columns per CTA
+constexpr int MLSTM_ROWS = 32;      // state rows per thread
+constexpr int MLSTM_TOK = 16;       // tokens staged at a time
+
+__device__ __forceinline__ float mlstm_logsigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+// num [rows][heads][vdim + 1] (the last column is n . q), mrow [rows][heads]
+__global__ void __launch_bounds__(MLSTM_COLS * 8)
+mlstm_scan_kernel(MlstmArgs a, const int* __restrict__ seq_row0, const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot,
+                  float* __restrict__ num, float* __restrict__ mrow) {
+  extern __shared__ float dyn_smem[];
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int tx = threadIdx.x, ty = threadIdx.y, NS = blockDim.y;
+  const int tid = ty * MLSTM_COLS + tx, nthreads = MLSTM_COLS * NS;
+  const int dpad = NS * MLSTM_ROWS;
+  float* q_s = dyn_smem;                            // [TOK][dpad], zero beyond dim
+  float* k_s = q_s + MLSTM_TOK * dpad;              // [TOK][dpad]
+  float* v_s = k_s + MLSTM_TOK * dpad;              // [TOK][COLS] the tile's values; 1 for the normaliser column
+  float* gi_s = v_s + MLSTM_TOK * MLSTM_COLS;       // [TOK] log input gates, then exp(i - m_t)
+  float* gf_s = gi_s + MLSTM_TOK;                   // [TOK] log forget gates, then exp(f + m_(t-1) - m_t)
+  float* m_s = gf_s + MLSTM_TOK;                    // [TOK + 1] m before the chunk, then after each token
+  float* red_s = m_s + MLSTM_TOK + 1;               // [TOK][NS][COLS] partial read-outs
+  const int row0 = seq_row0[s], len = seq_row0[s + 1] - row0, pos0 = seq_pos0[s];
+  const int col = blockIdx.z * MLSTM_COLS + tx;     // 0 .. vdim (vdim: the normaliser)
+  const bool live = col <= a.vdim;
+  const int cols = a.vdim + 1;
+  float* slot = a.state + (long long)seq_slot[s] * a.slot_stride + (long long)h * (a.dim + 1) * cols;
+  float S[MLSTM_ROWS];
+#pragma unroll
+  for (int dd = 0; dd < MLSTM_ROWS; ++dd) {
+    const int d = ty * MLSTM_ROWS + dd;
+    S[dd] = (pos0 > 0 && live && d < a.dim) ? slot[(long long)d * cols + col] : 0.f;
+  }
+  // every column tile keeps its own copy of m in the state's last row (at its first column): no CTA reads what another one writes
+  float* m_slot = slot + (long long)a.dim * cols + blockIdx.z * MLSTM_COLS;
+  if (tid == 0) m_s[0] = pos0 > 0 ? *m_slot : 0.f;
+  for (int c0 = 0; c0 < len; c0 += MLSTM_TOK) {
+    const int nt = len - c0 < MLSTM_TOK ? len - c0 : MLSTM_TOK;
+    __syncthreads();      // the previous chunk has been read
+    for (int i = tid; i < nt * dpad; i += nthreads) {
+      const int t = i / dpad, d = i % dpad;
+      const float* row = a.proj + (long long)(row0 + c0 + t) * a.ld;
+      q_s[i] = d < a.dim ? row[a.q_off + h * a.dim + d] * a.q_scale : 0.f;
+      k_s[i] = d < a.dim ? row[a.k_off + h * a.dim + d] : 0.f;
+    }
+    for (int i = tid; i < nt * MLSTM_COLS; i += nthreads) {
+      const int t = i / MLSTM_COLS, c = blockIdx.z * MLSTM_COLS + i % MLSTM_COLS;
+      const float* row = a.proj + (long long)(row0 + c0 + t) * a.ld;
+      v_s[i] = c < a.vdim ? row[a.v_off + h * a.vdim + c] : (c == a.vdim ? 1.f : 0.f);
+    }
+    if (tid < nt) {
+      const float* row = a.proj + (long long)(row0 + c0 + tid) * a.ld;
+      gi_s[tid] = a.gate_cap * tanhf((row[a.i_off + h] + a.i_bias[h]) / a.gate_cap);
+      gf_s[tid] = mlstm_logsigmoid(a.gate_cap * tanhf((row[a.f_off + h] + a.f_bias[h]) / a.gate_cap));
+    }
+    __syncthreads();
+    if (tid == 0) {
+      float m = m_s[0];
+      for (int t = 0; t < nt; ++t) {
+        m = fmaxf(gf_s[t] + m, gi_s[t]);
+        m_s[t + 1] = m;
+      }
+    }
+    __syncthreads();
+    if (tid < nt) {
+      const float keep = expf(gf_s[tid] + m_s[tid] - m_s[tid + 1]), take = expf(gi_s[tid] - m_s[tid + 1]);
+      gf_s[tid] = keep;
+      gi_s[tid] = take;
+      if (blockIdx.z == 0) mrow[(long long)(row0 + c0 + tid) * a.heads + h] = m_s[tid + 1];
+    }
+    __syncthreads();
+    float acc[MLSTM_TOK];
+#pragma unroll
+    for (int t = 0; t < MLSTM_TOK; ++t) {
+      acc[t] = 0.f;
+      if (t < nt) {
+        const float keep = gf_s[t], kv = gi_s[t] * v_s[t * MLSTM_COLS + tx];
+        const float* kq = k_s + t * dpad + ty * MLSTM_ROWS;
+        const float* qq = q_s + t * dpad + ty * MLSTM_ROWS;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+        for (int dd = 0; dd < MLSTM_ROWS; dd += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kq + dd);
+          const float4 q4 = *reinterpret_cast<const float4*>(qq + dd);
+          S[dd] = fmaf(keep, S[dd], k4.x * kv);
+          S[dd + 1] = fmaf(keep, S[dd + 1], k4.y * kv);
+          S[dd + 2] = fmaf(keep, S[dd + 2], k4.z * kv);
+          S[dd + 3] = fmaf(keep, S[dd + 3], k4.w * kv);
+          a0 = fmaf(S[dd], q4.x, a0);
+          a1 = fmaf(S[dd + 1], q4.y, a1);
+          a2 = fmaf(S[dd + 2], q4.z, a2);
+          a3 = fmaf(S[dd + 3], q4.w, a3);
+        }
+        acc[t] = (a0 + a1) + (a2 + a3);
+      }
+    }
+    if (NS > 1) {
+#pragma unroll
+      for (int t = 0; t < MLSTM_TOK; ++t)
+        if (t < nt) red_s[(t * NS + ty) * MLSTM_COLS + tx] = acc[t];
+      __syncthreads();
+      for (int i = tid; i < nt * MLSTM_COLS; i += nthreads) {
+        const int t = i / MLSTM_COLS, c = i % MLSTM_COLS;
+        const int cc = blockIdx.z * MLSTM_COLS + c;
+        if (cc <= a.vdim) {
+          float v = 0.f;
+          for (int y = 0; y < NS; ++y) v += red_s[(t * NS + y) * MLSTM_COLS + c];
+          num[((long long)(row0 + c0 + t) * a.heads + h) * cols + cc] = v;
+        }
+      }
+    } else if (live) {
+#pragma unroll
+      for (int t = 0; t < MLSTM_TOK; ++t)
+        if (t < nt) num[((long long)(row0 + c0 + t) * a.heads + h) * cols + col] = acc[t];
+    }
+    if (tid == 0) m_s[0] = m_s[nt];      // read again only after the next chunk's first barrier
+  }
+  if (live) {
+#pragma unroll
+    for (int dd = 0; dd < MLSTM_ROWS; ++dd) {
+      const int d = ty * MLSTM_ROWS + dd;
+      if (d < a.dim) slot[(long long)d * cols + col] = S[dd];
+    }
+  }
+  __syncthreads();
+  if (tid == 0) *m_slot = m_s[0];
+}
+
+constexpr int MLSTM_FIN_WARPS = 4;
+__global__ void __launch_bounds__(MLSTM_FIN_WARPS * 32)
+mlstm_finish_kernel(MlstmArgs a, int R, const float* __restrict__ num, const float* __restrict__ mrow) {
+  const int item = blockIdx.x * MLSTM_FIN_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (item >= R * a.heads) return;
+  const int r = item / a.heads, h = item % a.heads;
+  const int cols = a.vdim + 1;
+  const float* nr = num + (long long)item * cols;
+  const float den = fmaxf(fabsf(nr[a.vdim]), expf(-mrow[item])) + 1e-6f;
+  float ss = 0.f;
+  for (int c = lane; c < a.vdim; c += 32) {
+    const float o = nr[c] / den;
+    ss = fmaf(o, o, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float inv = 1.0f / sqrtf(ss / (float)a.vdim + a.eps);
+  const float* g = a.proj + (long long)r * a.ld + a.g_off + h * a.vdim;
+  for (int c = lane; c < a.vdim; c += 32) {
+    float v = nr[c] / den * inv;
+    if (a.out_gain != nullptr) v *= a.out_gain[h * a.vdim + c];
+    v *= 1.0f / (1.0f + expf(-g[c]));
+    const long long at = (long long)r * a.ldo + h * a.vdim + c;
+    if (a.out_fp32) reinterpret_cast<float*>(a.out)[at] = v;
+    else reinterpret_cast<bf16*>(a.out)[at] = __float2bfloat16(v);
+  }
+}
+
+}  // namespace lp
+
+using namespace lp;
+
+extern "C" size_t lp_mlstm_workspace_bytes(int rows, int heads, int vdim) {
+  return (size_t)rows * heads * (vdim + 2) * sizeof(float);
+}
+
+extern "C" int lp_mlstm(const lp_mlstm_desc* d, int n_seqs, int R, const int* seq_row0, const int* seq_pos0, const int* seq_slot,
+                        void* ws, size_t ws_bytes, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(d != nullptr && d->proj != nullptr && d->i_bias != nullptr && d->f_bias != nullptr && d->state != nullptr && d->out != nullptr,
+             "lp_mlstm: null operand");
+  LP_REQUIRE(d->heads > 0 && d->dim > 0 && d->vdim > 0 && d->dim <= 7 * MLSTM_ROWS, "lp_mlstm: bad sizes heads=%d dim=%d (at most %d) vdim=%d",
+             d->heads, d->dim, 7 * MLSTM_ROWS, d->vdim);
+  LP_REQUIRE(d->gate_cap > 0.f, "lp_mlstm: gate_cap must be positive");
+  LP_REQUIRE(d->slot_stride >= (long long)d->heads * (d->dim + 1) * (d->vdim + 1), "lp_mlstm: a slot is smaller than the state");
+  LP_REQUIRE(seq_row0 != nullptr && seq_pos0 != nullptr && seq_slot != nullptr && n_seqs >= 0 && R >= 0, "lp_mlstm: bad batch tables");
+  if (n_seqs == 0 || R == 0) return 0;
+  LP_REQUIRE(ws != nullptr && ws_bytes >= lp_mlstm_workspace_bytes(R, d->heads, d->vdim), "lp_mlstm: workspace too small");
+  MlstmArgs a;
+  a.proj = d->proj; a.ld = d->ld; a.q_off = d->q_off; a.k_off = d->k_off; a.v_off = d->v_off; a.g_off = d->g_off; a.i_off = d->i_off;
+  a.f_off = d->f_off; a.heads = d->heads; a.dim = d->dim; a.vdim = d->vdim; a.i_bias = d->i_bias; a.f_bias = d->f_bias;
+  a.gate_cap = d->gate_cap; a.q_scale = d->q_scale; a.eps = d->eps; a.out_gain = d->out_gain; a.state = d->state;
+  a.slot_stride = d->slot_stride; a.out = d->out; a.ldo = d->ldo; a.out_fp32 = d->out_fp32;
+  float* num = reinterpret_cast<float*>(ws);
+  float* mrow = num + (size_t)R * d->heads * (d->vdim + 1);
+  const int ns = (d->dim + MLSTM_ROWS - 1) / MLSTM_ROWS;
+  const size_t smem = ((size_t)2 * MLSTM_TOK * ns * MLSTM_ROWS + MLSTM_TOK * MLSTM_COLS + 3 * MLSTM_TOK + 1 +
+                       (size_t)MLSTM_TOK * ns * MLSTM_COLS + 3) * sizeof(float);      // < 48 kB for every dim allowed
+  mlstm_scan_kernel<<<dim3(n_seqs, d->heads, (d->vdim + 1 + MLSTM_COLS - 1) / MLSTM_COLS), dim3(MLSTM_COLS, ns), smem, stream>>>(
+      a, seq_row0, seq_pos0, seq_slot, num, mrow);
+  LP_CHECK_CUDA(cudaGetLastError());
+  mlstm_finish_kernel<<<(R * d->heads + MLSTM_FIN_WARPS - 1) / MLSTM_FIN_WARPS, MLSTM_FIN_WARPS * 32, 0, stream>>>(a, R, num, mrow);
+  LP_CHECK_CUDA(cudaGetLastError());
+  note_launch(2);
+  return 0;
+}

@@ -6,6 +6,8 @@
 //                    `keep_groups` best groups stay eligible (the others count as minus infinity); the `top` eligible experts with the
 //                    largest choice scores are chosen, ties to the lower index; weights = chosen s / (sum of chosen s + 1e-20).
 //                    Optionally one more row of weights gives a per-token sigmoid gate (for a shared expert).
+//   lp_moe_route_softmax  the plain token-choice router on the same kernel: logits z = W_router h + bias, the `top` largest logits are
+//                    chosen (ties to the lower index), weights = softmax over the chosen logits only.
 //   lp_moe_align     sorts the (token, choice) pairs by expert into a row space where every expert's segment is padded to whole
 //                    64-row tiles (the tile of lp_linear_grouped): tile_group[tile] = expert or -1, sorted_token[row] = token or -1,
 //                    pair_row[token * top + k] = the pair's row.  Sizes stay on the device: no host synchronisation.
@@ -38,7 +40,8 @@ template <typename HT>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const HT* __restrict__ h, long long ldh, int T, int D, const bf16* __restrict__ w_router, long long ldw, int E,
                  const float* __restrict__ correction, int n_groups, int keep_groups, int top, const bf16* __restrict__ w_gate,
-                 int* __restrict__ idx_out, float* __restrict__ w_out, float* __restrict__ gate_out) {
+                 int* __restrict__ idx_out, float* __restrict__ w_out, float* __restrict__ gate_out, int softmax_mode,
+                 const float* __restrict__ logit_bias) {
   __shared__ float sc[MOE_MAX_EXPERTS];   // sigmoid scores
   __shared__ float ch[MOE_MAX_EXPERTS];   // choice scores (minus infinity once taken or not eligible)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -65,7 +68,9 @@ moe_route_kernel(const HT* __restrict__ h, long long ldh, int T, int D, const bf
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     const float s = 1.0f / (1.0f + expf(-acc));
     if (lane == 0) {
-      if (e < E) {
+      if (softmax_mode) {      // the logit itself is score and choice
+        sc[e] = ch[e] = acc + (logit_bias != nullptr ? logit_bias[e] : 0.f);
+      } else if (e < E) {
         sc[e] = s;
         ch[e] = s + (correction != nullptr ? correction[e] : 0.f);
       } else {
@@ -99,6 +104,22 @@ moe_route_kernel(const HT* __restrict__ h, long long ldh, int T, int D, const bf
     for (int g = 0; g < n_groups; ++g)
       if (!kept[g])
         for (int i = 0; i < gs; ++i) ch[g * gs + i] = -INFINITY;
+  }
+  if (softmax_mode) {
+    float mx = -INFINITY, sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+      int best = 0;
+      for (int e = 1; e < E; ++e)
+        if (ch[e] > ch[best]) best = e;
+      idx_out[(long long)t * top + k] = best;
+      if (k == 0) mx = sc[best];      // the first choice is the largest logit
+      const float p = expf(sc[best] - mx);
+      w_out[(long long)t * top + k] = p;
+      sum += p;
+      ch[best] = -INFINITY;
+    }
+    for (int k = 0; k < top; ++k) w_out[(long long)t * top + k] /= sum;
+    return;
   }
   float sum = 0.f;
   for (int k = 0; k < top; ++k) {
@@ -178,11 +199,30 @@ extern "C" int lp_moe_route(const void* h, long long ldh, int h_fp32, int T, int
   if (h_fp32)
     moe_route_kernel<float><<<grid, ROUTE_WARPS * 32, 0, stream>>>(reinterpret_cast<const float*>(h), ldh, T, D,
         reinterpret_cast<const bf16*>(w_router), ldw, E, correction, n_groups, keep_groups, top, reinterpret_cast<const bf16*>(w_gate),
-        idx_out, w_out, gate_out);
+        idx_out, w_out, gate_out, 0, nullptr);
   else
     moe_route_kernel<bf16><<<grid, ROUTE_WARPS * 32, 0, stream>>>(reinterpret_cast<const bf16*>(h), ldh, T, D,
         reinterpret_cast<const bf16*>(w_router), ldw, E, correction, n_groups, keep_groups, top, reinterpret_cast<const bf16*>(w_gate),
-        idx_out, w_out, gate_out);
+        idx_out, w_out, gate_out, 0, nullptr);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_moe_route_softmax(const void* h, long long ldh, int h_fp32, int T, int D, const void* w_router, long long ldw, int E,
+                                    const float* logit_bias, int top, int* idx_out, float* w_out, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(h != nullptr && w_router != nullptr && idx_out != nullptr && w_out != nullptr, "lp_moe_route_softmax: null operand");
+  LP_REQUIRE(E > 0 && E <= MOE_MAX_EXPERTS && top > 0 && top <= E, "lp_moe_route_softmax: experts=%d top=%d (at most %d experts)", E, top,
+             MOE_MAX_EXPERTS);
+  if (T <= 0) return 0;
+  const unsigned grid = (unsigned)T;
+  if (h_fp32)
+    moe_route_kernel<float><<<grid, ROUTE_WARPS * 32, 0, stream>>>(reinterpret_cast<const float*>(h), ldh, T, D,
+        reinterpret_cast<const bf16*>(w_router), ldw, E, nullptr, 1, 1, top, nullptr, idx_out, w_out, nullptr, 1, logit_bias);
+  else
+    moe_route_kernel<bf16><<<grid, ROUTE_WARPS * 32, 0, stream>>>(reinterpret_cast<const bf16*>(h), ldh, T, D,
+        reinterpret_cast<const bf16*>(w_router), ldw, E, nullptr, 1, 1, top, nullptr, idx_out, w_out, nullptr, 1, logit_bias);
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -367,7 +367,13 @@ struct LatArgs {
   float* cache; int page_size;
   const int* page_table; int max_pages;
   int window; float scale;
+  const float* sink;                      // [heads] or null: exp(sink_h) joins the softmax denominator (no key, no value, not scaled)
+  const float* gate; long long ldg;       // [rows, ldg] or null: head h's output is multiplied by sigmoid(gate[r, h])
 };
+
+__device__ __forceinline__ float lat_gate(const LatArgs& a, int r, int h) {
+  return a.gate != nullptr ? 1.0f / (1.0f + expf(-a.gate[(long long)r * a.ldg + h])) : 1.0f;
+}
 
 __device__ __forceinline__ float* lat_cache_row(const LatArgs& a, int seq, int pos) {
   const int page = a.page_table[(long long)seq * a.max_pages + pos / a.page_size];
@@ -434,7 +440,9 @@ latent_attend_kernel(LatArgs a, int R, const int* __restrict__ row_seq, const in
     acc[i] = 0.f;
   }
   const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
-  float mx = -INFINITY, den = 0.f;
+  // the sink is a key without a value whose score is sink_h as it stands: warp 0 starts from it
+  const bool sunk = a.sink != nullptr && warp == 0;
+  float mx = sunk ? a.sink[h] : -INFINITY, den = sunk ? 1.f : 0.f;
   // two keys per turn: their score reductions overlap, one rescale of the running sums serves both
   for (int j = lo + warp; j <= pos; j += 2 * LAT_WARPS) {
     const bool two = j + LAT_WARPS <= pos;
@@ -488,7 +496,7 @@ latent_attend_kernel(LatArgs a, int R, const int* __restrict__ row_seq, const in
     f[w] = s_den[w] > 0.f ? expf(s_mx[w] - top) : 0.f;      // a warp without keys contributes nothing
     total = fmaf(s_den[w], f[w], total);
   }
-  const float inv = 1.0f / total;
+  const float inv = lat_gate(a, r, h) / total;
   for (int c = threadIdx.x; c < a.kv_rank; c += blockDim.x) {
     float v = 0.f;
 #pragma unroll
@@ -523,7 +531,7 @@ latent_attend_rows_kernel(LatArgs a, int R, const int* __restrict__ row_seq, con
     acc[i] = 0.f;
   }
   const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
-  float mx = -INFINITY, den = 0.f;
+  float mx = a.sink != nullptr ? a.sink[h] : -INFINITY, den = a.sink != nullptr ? 1.f : 0.f;
   // two keys per turn: their score reductions overlap, one rescale of the running sums serves both
   for (int j = lo; j <= pos; j += 2 * 1) {
     const bool two = j + 1 <= pos;
@@ -558,7 +566,7 @@ latent_attend_rows_kernel(LatArgs a, int R, const int* __restrict__ row_seq, con
     for (int i = 0; i < NR; ++i) acc[i] = fmaf(p1, cv1[i], fmaf(p0, cv0[i], acc[i] * corr));
     mx = mn;
   }
-  const float inv = 1.0f / den;
+  const float inv = lat_gate(a, r, h) / den;
 #pragma unroll
   for (int i = 0; i < NR; ++i) {
     const int c = lane + 32 * i;
@@ -611,6 +619,7 @@ static int fill_lat(LatArgs& a, const lp_latent_desc* d) {
   a.inv_freq = d->inv_freq; a.rot_dims = d->rot_dims; a.rot_layout = d->rot_layout; a.rot_mscale = d->rot_mscale;
   a.cache = d->cache; a.page_size = d->page_size; a.page_table = d->page_table; a.max_pages = d->max_pages;
   a.window = d->window; a.scale = d->scale;
+  a.sink = d->sink; a.gate = d->gate; a.ldg = d->ldg;
   return 0;
 }
 

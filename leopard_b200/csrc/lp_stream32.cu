@@ -6,6 +6,12 @@
 //                       `accum` — added to another fp32 matrix: the sandwich-norm residual update x <- x + norm(sublayer(x)) in one pass.
 //   lp_glu_f32          elementwise epilogues for matrix products that ran elsewhere: xIELU, squared relu, silu(gate) * up.
 //   lp_axpy_f32         y <- y + alpha x, the residual update after such a product.
+//   lp_add_positions_f32  x[r, 2i] += sin(p f_i), x[r, 2i + 1] += cos(p f_i) with p the row's position: absolute sinusoidal positions
+//                       added to the stream (angles in fp32 from an fp32 frequency table, accurate sincosf).
+//   lp_add_row_f32      x[r, :] += v for every row (a learned vector that marks a pass of a looped stack).
+//   lp_token_shift_f32  y_t = h_t + (h_(t-1) - h_t) * mu per channel, with h the rows as they came in; the row before a request's
+//                       first row of this step comes from the request's slot (zeros at position 0), and the slot then takes the
+//                       request's last row.
 //
 // One warp per row, statistics and normalisation in fp32; the row is read twice (the second read hits L1 / L2).
 #include "lp_host.h"
@@ -80,9 +86,95 @@ __global__ void axpy_f32_kernel(float* __restrict__ y, long long ldy, const floa
   y[(long long)m * ldy + n] = fmaf(alpha, x[(long long)m * ldx + n], y[(long long)m * ldy + n]);
 }
 
+// pair i of a row: (sin, cos) of position * freq[i]; an odd width leaves the last sine without its cosine
+__global__ void add_positions_f32_kernel(float* __restrict__ x, long long ldx, int R, int D, const int* __restrict__ row_pos,
+                                         const float* __restrict__ freq) {
+  const int r = blockIdx.x;
+  if (r >= R) return;
+  const float p = (float)row_pos[r];
+  float* xr = x + (long long)r * ldx;
+  for (int i = threadIdx.x; 2 * i < D; i += blockDim.x) {
+    float s, c;
+    sincosf(p * freq[i], &s, &c);
+    xr[2 * i] += s;
+    if (2 * i + 1 < D) xr[2 * i + 1] += c;
+  }
+}
+
+__global__ void add_row_f32_kernel(float* __restrict__ x, long long ldx, const float* __restrict__ v, int M, int N) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)M * N) return;
+  const int m = (int)(i / N), n = (int)(i % N);
+  x[(long long)m * ldx + n] += v[n];
+}
+
+// One thread per (row, channel).  Only the thread of a request's FIRST row touches the request's slot: it reads the carried row
+// and then stores the request's last row of this step there, so no other thread of the launch reads what it writes.
+template <typename OT>
+__global__ void token_shift_kernel(const float* __restrict__ h, long long ldh, const float* __restrict__ mu, int R, int D,
+                                   const int* __restrict__ row_seq, const int* __restrict__ row_pos, const int* __restrict__ seq_row0,
+                                   const int* __restrict__ seq_slot, float* __restrict__ state, long long slot_stride,
+                                   OT* __restrict__ out, long long ldo) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)R * D) return;
+  const int r = (int)(i / D), c = (int)(i % D);
+  const int s = row_seq[r];
+  const float cur = h[(long long)r * ldh + c];
+  float prev;
+  if (r == seq_row0[s]) {
+    float* slot = state + (long long)seq_slot[s] * slot_stride;
+    prev = row_pos[r] > 0 ? slot[c] : 0.f;
+    slot[c] = h[(long long)(seq_row0[s + 1] - 1) * ldh + c];
+  } else {
+    prev = h[(long long)(r - 1) * ldh + c];
+  }
+  st32(out + (long long)r * ldo + c, fmaf(prev - cur, mu[c], cur));
+}
+
 }  // namespace lp
 
 using namespace lp;
+
+extern "C" int lp_add_positions_f32(float* x, long long ldx, int R, int D, const int* row_pos, const float* freq, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(x != nullptr && row_pos != nullptr && freq != nullptr && R >= 0 && D > 0, "lp_add_positions_f32: bad arguments");
+  if (R == 0) return 0;
+  add_positions_f32_kernel<<<R, 128, 0, stream>>>(x, ldx, R, D, row_pos, freq);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_add_row_f32(float* x, long long ldx, const float* v, int M, int N, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(x != nullptr && v != nullptr && M >= 0 && N > 0, "lp_add_row_f32: bad arguments");
+  if (M == 0) return 0;
+  add_row_f32_kernel<<<(unsigned)(((long long)M * N + 255) / 256), 256, 0, stream>>>(x, ldx, v, M, N);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_token_shift_f32(const float* h, long long ldh, const float* mu, int R, int D, const int* row_seq, const int* row_pos,
+                                  const int* seq_row0, const int* seq_slot, float* state, long long slot_stride, void* out,
+                                  long long ldo, int out_fp32, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(h != nullptr && mu != nullptr && out != nullptr && state != nullptr && row_seq != nullptr && row_pos != nullptr &&
+                 seq_row0 != nullptr && seq_slot != nullptr && R >= 0 && D > 0 && slot_stride >= D,
+             "lp_token_shift_f32: bad arguments");
+  LP_REQUIRE(h != out, "lp_token_shift_f32: a row reads its neighbour as it came in, so it cannot run in place");
+  if (R == 0) return 0;
+  const unsigned grid = (unsigned)(((long long)R * D + 255) / 256);
+  if (out_fp32)
+    token_shift_kernel<float><<<grid, 256, 0, stream>>>(h, ldh, mu, R, D, row_seq, row_pos, seq_row0, seq_slot, state, slot_stride,
+                                                        reinterpret_cast<float*>(out), ldo);
+  else
+    token_shift_kernel<bf16><<<grid, 256, 0, stream>>>(h, ldh, mu, R, D, row_seq, row_pos, seq_row0, seq_slot, state, slot_stride,
+                                                       reinterpret_cast<bf16*>(out), ldo);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
 
 extern "C" int lp_embed_rows_f32(const int* ids, int R, const void* table, long long ldt, int vocab, float scale, float* out, long long ldo,
                                  int D, void* stream_) {

@@ -9,6 +9,9 @@
 //                optional rotation of the values by their own position with the head output turned back by the query's position
 //                (the weighted sum then depends on the distances i - j only)
 //
+//   mixing       talk: the softmax weights of the heads are mixed before they meet the values, weight_h <- sum_g talk[h, g] weight_g;
+//                an output gate sigmoid(g) taken from the fused projection multiplies the heads' outputs
+//
 //   lp_window_attn_prep   one CTA per row: sums of squares per head, then every (pair | single) element of q, k, v is normalised,
 //                         rotated and written: q in place, k and v into the request's page.
 //   lp_window_attn_pool   one CTA per completed block: the mean of its P cached rows -> the block's row in the pooled pool.
@@ -18,6 +21,9 @@
 //                         time), the warp agrees on the running maximum, then the 32 values are accumulated with the
 //                         lanes spread over vdim (weights and row addresses broadcast through shared memory).  The CTA's warps take every W-th tile
 //                         and merge their (maximum, denominator, sum) triples at the end.  All of it in fp32.
+//   lp_window_attn_talk   one CTA per row and ALL heads, two passes over the visible keys in tiles of 64: the first finds every head's
+//                         softmax maximum and denominator, the second computes the scores again, normalises them, mixes them over
+//                         the heads in shared memory and adds the values with the mixed weights.
 //   lp_window_attn_tiles  the same for prompts, a CTA per tile of 2 or 4 consecutive rows of a request: the rows share every key and
 //                         value row the tile reads, each (row, key) pair masked by the row's own rule.
 #include "lp_host.h"
@@ -37,6 +43,8 @@ struct WinArgs {
   float* pooled; const int* pooled_table; int max_pooled_pages; int pool;
   int window, keep_first;
   float scale, softcap; int sink;
+  const float* q_bias; const float* k_bias; const float* v_bias; int v_norm;
+  const float* talk; int g_off;
 };
 
 __device__ __forceinline__ float* win_token_row(const WinArgs& a, int seq, int pos) {
@@ -89,6 +97,28 @@ window_attn_prep_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const
   const int seq = row_seq[r], pos = row_pos[r];
   float* x = a.qkv + (long long)r * a.ld;
   const int units = a.heads + a.kv_heads;
+  // biases of the projections: added in place before anything reads the row
+  if (a.q_bias != nullptr || a.k_bias != nullptr || a.v_bias != nullptr) {
+    if (a.q_bias != nullptr)
+      for (int i = tid; i < a.heads * a.dim; i += blockDim.x) x[a.q_off + i] += a.q_bias[i];
+    if (a.k_bias != nullptr)
+      for (int i = tid; i < a.kv_heads * a.dim; i += blockDim.x) x[a.k_off + i] += a.k_bias[i];
+    if (a.v_bias != nullptr)
+      for (int i = tid; i < a.kv_heads * a.vdim; i += blockDim.x) x[a.v_off + i] += a.v_bias[i];
+    __syncthreads();
+  }
+  float* s_vss = s_ss + units + 2;      // [kv_heads] sums of squares of the value heads
+  if (a.v_norm) {
+    for (int u = warp; u < a.kv_heads; u += n_warps) {
+      const float* src = x + a.v_off + u * a.vdim;
+      float ss = 0.f;
+      for (int d = lane; d < a.vdim; d += 32) ss = fmaf(src[d], src[d], ss);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) s_vss[u] = ss;
+    }
+    __syncthreads();
+  }
   if (a.norm_mode != LP_QKNORM_NONE) {
     for (int u = warp; u < units; u += n_warps) {
       const float* src = u < a.heads ? x + a.q_off + u * a.dim : x + a.k_off + (u - a.heads) * a.dim;
@@ -158,17 +188,18 @@ window_attn_prep_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const
     const int g = it / vper, e = it % vper;
     const float* src = x + a.v_off + g * a.vdim;
     float* dst = crow + a.kv_heads * a.dim + g * a.vdim;
+    const float vinv = a.v_norm ? 1.0f / sqrtf(s_vss[g] / (float)a.vdim + a.eps) : 1.f;      // unit RMS per value head, cached so
     if (e < vhalf) {
       int d0, d1;
       win_pair(a.v_rot_layout, vhalf, e, d0, d1);
       float s, c;
       sincosf((float)pos * a.v_inv_freq[e], &s, &c);
-      const float u0 = src[d0], u1 = src[d1];
+      const float u0 = src[d0] * vinv, u1 = src[d1] * vinv;
       dst[d0] = u0 * c - u1 * s;
       dst[d1] = u1 * c + u0 * s;
     } else {
       const int d = vrot + (e - vhalf);
-      dst[d] = src[d];
+      dst[d] = src[d] * vinv;
     }
   }
 }
@@ -632,6 +663,181 @@ window_attn_tile_kernel(WinArgs a, int n_chunks, const int* __restrict__ chunk_s
   }
 }
 
+
+// Talking heads: the softmax weights of all heads are mixed, weight_h(i, j) <- sum_g talk[h, g] weight_g(i, j), before head h applies
+// them to the values of its own key / value head — so a row needs the NORMALISED weights of every head at every key.  One CTA per
+// row and all heads; the visible keys (the same index space as above: kept tokens, pooled blocks, window) are walked twice in tiles
+// of TALK_TILE keys.  Pass 1: scores of the tile for every head -> running maximum and denominator per head.  Pass 2: the same
+// scores again (the same arithmetic, so the same numbers), weights = exp(score - max) / denominator, mixed over the heads in shared
+// memory, then every thread adds the tile's values to the (head, value channel) sums it owns.  Nothing is rescaled in pass 2: the
+// weights are final.  An output gate, when the description names one, multiplies the sums by sigmoid(g) on the way out.
+constexpr int TALK_TILE = 64;
+constexpr int TALK_THREADS = 256;
+constexpr int TALK_MAX_ACC = 32;      // heads * vdim <= TALK_THREADS * TALK_MAX_ACC
+
+// scores of one tile -> p_s[h][jj] (scaled and capped); a thread takes one key and up to four query heads of one key / value head
+__device__ __forceinline__ void talk_tile_scores(const WinArgs& a, const WinVisible& vis, int seq, int t0, int cnt, const float* q_s,
+                                                 float* p_s, const float** row_s, int tid, int nthreads) {
+  const int ratio = a.heads / a.kv_heads;
+  const int hgroups = (ratio + 3) / 4;      // groups of at most four query heads per key / value head
+  for (int jj = tid; jj < cnt; jj += nthreads) row_s[jj] = win_visible_row(a, vis, seq, t0 + jj);
+  __syncthreads();
+  const bool vec = (a.dim % 4 == 0) && (a.vdim % 4 == 0);
+  for (int it = tid; it < a.kv_heads * hgroups * cnt; it += nthreads) {
+    const int jj = it % cnt, u = it / cnt;
+    const int g = u / hgroups, h0 = g * ratio + (u % hgroups) * 4;
+    const int nh = (g + 1) * ratio - h0 < 4 ? (g + 1) * ratio - h0 : 4;
+    const float* kp = row_s[jj] + g * a.dim;
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (vec) {
+      for (int d = 0; d < a.dim; d += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kp + d);
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          if (h < nh) {
+            const float4 q4 = *reinterpret_cast<const float4*>(q_s + (h0 + h) * a.dim + d);
+            sc[h] = fmaf(q4.x, k4.x, sc[h]);
+            sc[h] = fmaf(q4.y, k4.y, sc[h]);
+            sc[h] = fmaf(q4.z, k4.z, sc[h]);
+            sc[h] = fmaf(q4.w, k4.w, sc[h]);
+          }
+        }
+      }
+    } else {
+      for (int d = 0; d < a.dim; ++d) {
+        const float kv = kp[d];
+#pragma unroll
+        for (int h = 0; h < 4; ++h)
+          if (h < nh) sc[h] = fmaf(q_s[(h0 + h) * a.dim + d], kv, sc[h]);
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      if (h < nh) {
+        float v = sc[h] * a.scale;
+        if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+        p_s[(h0 + h) * TALK_TILE + jj] = v;
+      }
+    }
+  }
+  __syncthreads();
+}
+
+template <int NACC>
+__global__ void __launch_bounds__(TALK_THREADS)
+window_attn_talk_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const int* __restrict__ row_pos, void* __restrict__ out,
+                        long long ldo, int out_fp32) {
+  extern __shared__ float dyn_smem[];
+  const int r = blockIdx.x;
+  if (r >= R) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthreads = blockDim.x, n_warps = blockDim.x >> 5;
+  const int H = a.heads, ratio = a.heads / a.kv_heads;
+  const float** row_s = reinterpret_cast<const float**>(dyn_smem);      // [TALK_TILE] cache row of each key of the tile
+  float* q_s = dyn_smem + 2 * TALK_TILE;        // [H][dim]
+  float* p_s = q_s + H * a.dim;                 // [H][TALK_TILE] scores, then weights
+  float* w_s = p_s + H * TALK_TILE;             // [H][TALK_TILE] mixed weights
+  float* m_s = w_s + H * TALK_TILE;             // [H] maxima
+  float* l_s = m_s + H;                         // [H] denominators, then their inverses
+  float* t_s = l_s + H;                         // [H][H] the mixing matrix
+  const int seq = row_seq[r], pos = row_pos[r];
+  const float* q = a.qkv + (long long)r * a.ld + a.q_off;
+  for (int i = tid; i < H * a.dim; i += nthreads) q_s[i] = q[i];
+  for (int i = tid; i < H * H; i += nthreads) t_s[i] = a.talk[i];
+  for (int h = tid; h < H; h += nthreads) {      // the sink is a key of score 0 without a value
+    m_s[h] = a.sink ? 0.f : -INFINITY;
+    l_s[h] = a.sink ? 1.f : 0.f;
+  }
+  __syncthreads();
+  const WinVisible vis = win_visible(a, pos);
+  // pass 1: maxima and denominators
+  for (int t0 = 0; t0 < vis.count; t0 += TALK_TILE) {
+    const int cnt = vis.count - t0 < TALK_TILE ? vis.count - t0 : TALK_TILE;
+    talk_tile_scores(a, vis, seq, t0, cnt, q_s, p_s, row_s, tid, nthreads);
+    for (int h = warp; h < H; h += n_warps) {
+      float top = -INFINITY;
+      for (int jj = lane; jj < cnt; jj += 32) top = fmaxf(top, p_s[h * TALK_TILE + jj]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+      const float mn = fmaxf(m_s[h], top);
+      float sum = 0.f;
+      for (int jj = lane; jj < cnt; jj += 32) sum += expf(p_s[h * TALK_TILE + jj] - mn);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      __syncwarp();
+      if (lane == 0) {
+        l_s[h] = fmaf(l_s[h], expf(m_s[h] - mn), sum);      // exp(-inf) = 0 on the first tile
+        m_s[h] = mn;
+      }
+    }
+    __syncthreads();
+  }
+  for (int h = tid; h < H; h += nthreads) l_s[h] = 1.0f / l_s[h];
+  __syncthreads();
+  // pass 2: final weights, mixed, times the values
+  float acc[NACC];
+#pragma unroll
+  for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
+  const int n_out = H * a.vdim;
+  const int v_base = a.kv_heads * a.dim;
+  for (int t0 = 0; t0 < vis.count; t0 += TALK_TILE) {
+    const int cnt = vis.count - t0 < TALK_TILE ? vis.count - t0 : TALK_TILE;
+    talk_tile_scores(a, vis, seq, t0, cnt, q_s, p_s, row_s, tid, nthreads);
+    for (int it = tid; it < H * cnt; it += nthreads) {
+      const int h = it / cnt, jj = it % cnt;
+      p_s[h * TALK_TILE + jj] = expf(p_s[h * TALK_TILE + jj] - m_s[h]) * l_s[h];
+    }
+    __syncthreads();
+    for (int it = tid; it < H * cnt; it += nthreads) {
+      const int h = it / cnt, jj = it % cnt;
+      float v = 0.f;
+      for (int g = 0; g < H; ++g) v = fmaf(t_s[h * H + g], p_s[g * TALK_TILE + jj], v);
+      w_s[h * TALK_TILE + jj] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) {
+      const int e = tid + i * nthreads;
+      if (e < n_out) {
+        const int h = e / a.vdim, c = e % a.vdim;
+        const int off = v_base + (h / ratio) * a.vdim + c;
+        const float* wh = w_s + h * TALK_TILE;
+        float v = acc[i];
+        for (int jj = 0; jj < cnt; ++jj) v = fmaf(wh[jj], row_s[jj][off], v);
+        acc[i] = v;
+      }
+    }
+    __syncthreads();
+  }
+  const float* gate = a.g_off >= 0 ? a.qkv + (long long)r * a.ld + a.g_off : nullptr;
+#pragma unroll
+  for (int i = 0; i < NACC; ++i) {
+    const int e = tid + i * nthreads;
+    if (e < n_out) {
+      float v = acc[i];
+      if (gate != nullptr) v *= 1.0f / (1.0f + expf(-gate[e]));
+      const long long at = (long long)r * ldo + e;
+      if (out_fp32) reinterpret_cast<float*>(out)[at] = v;
+      else reinterpret_cast<bf16*>(out)[at] = __float2bfloat16(v);
+    }
+  }
+}
+
+// the dynamic shared-memory limit is raised once per instantiation, and only when a launch needs it (no runtime call on the steady
+// path, so the steady path can be captured into a CUDA graph)
+template <int NACC>
+static int launch_window_attn_talk(const WinArgs& a, int R, const int* row_seq, const int* row_pos, void* out, long long ldo, int out_fp32,
+                                   size_t smem, cudaStream_t stream) {
+  static size_t have = 48 * 1024;
+  if (smem > have) {
+    LP_CHECK_CUDA(cudaFuncSetAttribute(window_attn_talk_kernel<NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    have = 200 * 1024;
+  }
+  window_attn_talk_kernel<NACC><<<R, TALK_THREADS, smem, stream>>>(a, R, row_seq, row_pos, out, ldo, out_fp32);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
 static int fill_win(WinArgs& a, const lp_window_attn_desc* d, bool need_q) {
   LP_REQUIRE(d != nullptr && d->cache != nullptr && d->page_table != nullptr, "lp_window_attn: null operand");
   LP_REQUIRE(!need_q || d->qkv != nullptr, "lp_window_attn: null projection");
@@ -644,7 +850,8 @@ static int fill_win(WinArgs& a, const lp_window_attn_desc* d, bool need_q) {
   LP_REQUIRE(d->v_inv_freq == nullptr || (d->v_rot_dims >= 0 && d->v_rot_dims <= d->vdim && d->v_rot_dims % 2 == 0),
              "lp_window_attn: v_rot_dims=%d must be even and <= vdim=%d", d->v_rot_dims, d->vdim);
   LP_REQUIRE(d->norm_mode >= LP_QKNORM_NONE && d->norm_mode <= LP_QKNORM_FULL, "lp_window_attn: bad norm mode %d", d->norm_mode);
-  LP_REQUIRE(d->norm_mode == LP_QKNORM_NONE || (d->q_gain != nullptr && d->k_gain != nullptr), "lp_window_attn: norm without gains");
+  LP_REQUIRE((d->q_gain != nullptr) == (d->k_gain != nullptr), "lp_window_attn: one norm gain without the other");
+  LP_REQUIRE(d->norm_mode != LP_QKNORM_NONE || d->q_gain == nullptr, "lp_window_attn: gains without a norm");
   LP_REQUIRE(d->pool >= 0 && (d->pool == 0 || (d->pooled != nullptr && d->pooled_table != nullptr && d->max_pooled_pages > 0)),
              "lp_window_attn: pooled blocks without their pool");
   LP_REQUIRE(d->keep_first >= 0, "lp_window_attn: keep_first < 0");
@@ -657,6 +864,8 @@ static int fill_win(WinArgs& a, const lp_window_attn_desc* d, bool need_q) {
   a.pooled = d->pooled; a.pooled_table = d->pooled_table; a.max_pooled_pages = d->max_pooled_pages; a.pool = d->pool;
   a.window = d->window; a.keep_first = d->keep_first;
   a.scale = d->scale; a.softcap = d->softcap; a.sink = d->sink;
+  a.q_bias = d->q_bias; a.k_bias = d->k_bias; a.v_bias = d->v_bias; a.v_norm = d->v_norm;
+  a.talk = d->talk; a.g_off = d->g_off;
   return 0;
 }
 
@@ -720,7 +929,7 @@ extern "C" int lp_window_attn_prep(const lp_window_attn_desc* d, int R, const in
   if (int rc = fill_win(a, d, true)) return rc;
   LP_REQUIRE(row_seq != nullptr && row_pos != nullptr, "lp_window_attn_prep: null operand");
   if (R <= 0) return 0;
-  const size_t smem = (size_t)(d->heads + d->kv_heads + 2) * sizeof(float);
+  const size_t smem = (size_t)(d->heads + 2 * d->kv_heads + 2) * sizeof(float);
   LP_REQUIRE(smem <= 48 * 1024, "lp_window_attn_prep: too many heads");
   window_attn_prep_kernel<<<R, WIN_PREP_THREADS, smem, stream>>>(a, R, row_seq, row_pos);
   note_launch();
@@ -757,6 +966,25 @@ extern "C" int lp_window_attn(const lp_window_attn_desc* d, int R, const int* ro
   if (ratio % 4 == 0) return launch_window_attn<4>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
   if (ratio % 2 == 0) return launch_window_attn<2>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
   return launch_window_attn<1>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
+}
+
+extern "C" int lp_window_attn_talk(const lp_window_attn_desc* d, int R, const int* row_seq, const int* row_pos, void* out, long long ldo,
+                                   int out_fp32, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  WinArgs a;
+  if (int rc = fill_win(a, d, true)) return rc;
+  LP_REQUIRE(out != nullptr && row_seq != nullptr && row_pos != nullptr && d->talk != nullptr, "lp_window_attn_talk: null operand");
+  LP_REQUIRE(d->v_inv_freq == nullptr, "lp_window_attn_talk: rotated values are not mixed here");
+  if (R <= 0) return 0;
+  const int n_out = d->heads * d->vdim;
+  LP_REQUIRE(n_out <= TALK_THREADS * TALK_MAX_ACC, "lp_window_attn_talk: heads * vdim = %d > %d", n_out, TALK_THREADS * TALK_MAX_ACC);
+  const size_t smem = (2 * (size_t)TALK_TILE + (size_t)d->heads * d->dim + 2 * (size_t)d->heads * TALK_TILE + 2 * (size_t)d->heads +
+                       (size_t)d->heads * d->heads) * sizeof(float);
+  LP_REQUIRE(smem <= 200 * 1024, "lp_window_attn_talk: heads=%d dim=%d do not fit shared memory", d->heads, d->dim);
+  const int nacc = (n_out + TALK_THREADS - 1) / TALK_THREADS;
+  if (nacc <= 2) return launch_window_attn_talk<2>(a, R, row_seq, row_pos, out, ldo, out_fp32, smem, stream);
+  if (nacc <= 8) return launch_window_attn_talk<8>(a, R, row_seq, row_pos, out, ldo, out_fp32, smem, stream);
+  return launch_window_attn_talk<TALK_MAX_ACC>(a, R, row_seq, row_pos, out, ldo, out_fp32, smem, stream);
 }
 
 extern "C" int lp_window_attn_tiles(const lp_window_attn_desc* d, int R, const int* row_seq, const int* row_pos, int n_chunks,

@@ -50,6 +50,11 @@ def _ronelorn(path, **kw):
     return ronelorn.load(path, **kw)
 
 
+def _gavatar(path, **kw):
+    from . import gavatar
+    return gavatar.load(path, **kw)
+
+
 def _llava(path, **kw):
     from .hf import myLlavaForConditionalGeneration
     return myLlavaForConditionalGeneration.from_pretrained(path, **kw)
@@ -57,6 +62,7 @@ def _llava(path, **kw):
 
 register("Zudalorn", _zudalorn)
 register("Ronelorn", _ronelorn)
+register("Gavatar", _gavatar)
 register("LlavaForConditionalGeneration", _llava)
 register("myLlavaForConditionalGeneration", _llava)
 register("llava", _llava)

@@ -1,8 +1,9 @@
 """Decoder-only language models described as a LIST OF LAYERS, on the 32-bit residual-stream kernels.
 
 A model is a `SeqLMConfig`: vocabulary, width, norm epsilon and style, and a tuple of `LayerConfig`s, each naming its sequence mixer
-(`RetentionConfig`, `LatentAttentionConfig`, `WindowAttentionConfig` or `MinGRUConfig`) and its feed-forward (`DenseFFConfig`,
-`MoEConfig` or none); a layer may run on another layer's weights with a cache or state of its own.  Every mechanism is a
+(`RetentionConfig`, `LatentAttentionConfig`, `WindowAttentionConfig`, `MinGRUConfig` or `MLSTMConfig`) and its feed-forward
+(`DenseFFConfig`, `MoEConfig` or none); a layer may run on another layer's weights with a cache or state of its own (a looped stack
+is such a list), shift its mixer's input towards the previous token's, and add a learned vector to the stream before it runs.  Every mechanism is a
 separate native entry point with its constants as arguments (include/leopard_b200.h, "32-BIT RESIDUAL-STREAM MODELS"), so another
 design is another list.  The residual stream, norms, routers, rotary angles, attention scores and recurrent state are fp32; matrix
 products take bf16 weights and, in the serving precision, bf16 activations with fp32 accumulation ("bfloat16"), or fp32 activations
@@ -105,6 +106,9 @@ class LatentAttentionConfig:
     scale: float
     rot: RotaryConfig
     window: Optional[int] = None   # position i sees j with 0 <= i - j < window; None: every earlier position
+    q_rank: int = 0                # > 0: queries go through a normed latent of this size (mix.dq, mix.dq.norm, mix.uq) instead of mix.q
+    sink: bool = False             # exp(mix.sink[h]) joins head h's softmax denominator
+    head_gate: bool = False        # head h's output is multiplied by sigmoid(mix.g h)[h]
 
 
 @dataclass(frozen=True)
@@ -116,19 +120,34 @@ class WindowAttentionConfig:
     vdim: int
     scale: float
     rot: RotaryConfig
-    qk_norm: str = "none"          # RMS norm of q and k before rotation: "head" (per head, gain [dim]), "full" (whole projection), "none"
+    # RMS norm of q and k before rotation: "head" (per head, gain [dim]), "unit" (per head, no gain), "full" (whole projection), "none"
+    qk_norm: str = "none"
     window: Optional[int] = None   # position i sees j with 0 <= i - j < window; None: every earlier position
     keep_first: int = 0            # the first tokens of a request stay visible beyond the window
     pool: int = 0                  # > 0: blocks of this many tokens wholly before the window are seen as one mean key / value
     softcap: float = 0.0           # > 0: score <- softcap tanh(score / softcap)
     sink: bool = False             # one added to the softmax denominator
     value_rot: Optional[RotaryConfig] = None   # values rotated by their position, outputs turned back by the query's
+    bias: bool = False             # q, k and v projections have biases (mix.q.b, mix.k.b, mix.v.b)
+    value_norm: bool = False       # every value head is divided by its root mean square before it is cached
+    talking_heads: bool = False    # softmax weights mixed over the heads by mix.talk [heads, heads] before they meet the values
+    out_gate: bool = False         # the concatenated heads are multiplied by sigmoid(mix.g h)
 
 
 @dataclass(frozen=True)
 class MinGRUConfig:
     """Gated recurrence whose gates read only the current token (csrc/lp_mingru.cu)."""
     width: int
+
+
+@dataclass(frozen=True)
+class MLSTMConfig:
+    """Matrix memory with exponential gates and a running stabiliser (csrc/lp_mlstm.cu); the gates' pre-activations are capped by
+    gate_cap * tanh(. / gate_cap)."""
+    heads: int
+    dim: int
+    vdim: int
+    gate_cap: float
 
 
 @dataclass(frozen=True)
@@ -145,13 +164,20 @@ class MoEConfig:
     n_groups: int = 1
     keep_groups: int = 1
     shared_ff: int = 0             # 0: no shared expert
+    # "grouped_sigmoid": sigmoid scores, choice bias, best groups, weights = chosen scores / their sum;
+    # "softmax_top": logits + mlp.router.b, the largest are chosen, weights = softmax over the chosen logits
+    router: str = "grouped_sigmoid"
 
 
 @dataclass(frozen=True)
 class LayerConfig:
-    mixer: Union[RetentionConfig, LatentAttentionConfig, WindowAttentionConfig, MinGRUConfig]
+    mixer: Union[RetentionConfig, LatentAttentionConfig, WindowAttentionConfig, MinGRUConfig, MLSTMConfig]
     ff: Union[DenseFFConfig, MoEConfig, None]
     weights_of: Optional[int] = None   # run on that layer's tensors (mixer, feed-forward, norms); cache and state stay this layer's own
+    # the mixer reads h_t + (h_(t-1) - h_t) * shift per channel instead of h_t (h: the normed stream; the previous token's h is part of
+    # the request's state, zeros before the first token); the vector is the layer's tensor `shift`
+    token_shift: bool = False
+    add_before: Optional[Tuple[str, int]] = None   # (tensor, row): that row is added to the stream right before this layer runs
 
 
 @dataclass(frozen=True)
@@ -162,10 +188,12 @@ class SeqLMConfig:
     eps: float
     layers: Tuple[LayerConfig, ...]
     # "sandwich": x <- x + norm_b(sublayer(norm_a(x))), every norm with ONE gain; "pre": x <- x + residual_mult * sublayer(norm(x)),
-    # the norm's gain a vector stored around zero (x / rms * (1 + w))
+    # the norm's gain a vector stored around zero (x / rms * (1 + w)); "sandwich_vector": the sandwich form with such vector gains
     norm: str = "sandwich"
     residual_mult: float = 1.0
     embed_scale: float = 1.0
+    # > 0: absolute sinusoidal positions are added to the embedding, entries (2i, 2i + 1) = (sin, cos)(p * base^(-2i / width))
+    position_base: float = 0.0
 
 
 def softplus(x: float) -> float:
@@ -199,43 +227,83 @@ class SeqLMWeights:
         def one_plus(layer, key):           # a gain stored around zero
             return (1.0 + w(layer, key, (cfg.width,)).float()).contiguous().to(dev)
 
-        if cfg.norm not in ("sandwich", "pre"):
+        if cfg.norm not in ("sandwich", "pre", "sandwich_vector"):
             raise ValueError(f"unknown norm style {cfg.norm!r}")
         pre = cfg.norm == "pre"
+        vector = cfg.norm != "sandwich"
         D = cfg.width
         self.embed = mat(w(None, "embed", (cfg.vocab, D)))
         self.head = mat(w(None, "head", (cfg.vocab, D)))
-        self.final_gain = one_plus(None, "final.norm") if pre else num(None, "final.norm")
+        self.final_gain = one_plus(None, "final.norm") if vector else num(None, "final.norm")
+        if cfg.position_base > 0:      # frequencies in float64, rounded once
+            i2 = np.arange((D + 1) // 2, dtype=np.float64)
+            self.position_freq = torch.from_numpy((cfg.position_base ** (-2.0 * i2 / D)).astype(np.float32)).to(dev)
+        # vectors added to the stream before a layer: per layer of the list, also for one that runs on another layer's tensors
+        self.add_before: List[Optional[torch.Tensor]] = []
+        for lc in cfg.layers:
+            if lc.add_before is None:
+                self.add_before.append(None)
+            else:
+                key, row = lc.add_before
+                t = w(None, key)
+                if t.dim() != 2 or t.shape[1] != D or not 0 <= row < t.shape[0]:
+                    raise ValueError(f"{name(None, key)}: shape {tuple(t.shape)} has no row {row} of width {D}")
+                self.add_before.append(vec(t[row]))
         self.layers: List[Dict[str, object]] = []
         for i, lc in enumerate(cfg.layers):
             if lc.weights_of is not None:
                 j = lc.weights_of
                 if not 0 <= j < len(cfg.layers) or cfg.layers[j].weights_of is not None:
                     raise ValueError(f"layer {i}: weights_of = {j} must name a layer that has tensors of its own")
-                if (cfg.layers[j].mixer, cfg.layers[j].ff) != (lc.mixer, lc.ff):
+                if (cfg.layers[j].mixer, cfg.layers[j].ff, cfg.layers[j].token_shift) != (lc.mixer, lc.ff, lc.token_shift):
                     raise ValueError(f"layer {i} differs from layer {j}, whose weights it uses")
                 self.layers.append(None)              # linked below, once every owner is loaded
                 continue
-            lw: Dict[str, object] = {"norm1": one_plus(i, "norm1")} if pre else {k: num(i, k) for k in ("norm1", "norm1b")}
+            if pre:
+                lw: Dict[str, object] = {"norm1": one_plus(i, "norm1")}
+            elif vector:
+                lw = {k: one_plus(i, k) for k in ("norm1", "norm1b")}
+            else:
+                lw = {k: num(i, k) for k in ("norm1", "norm1b")}
+            if lc.token_shift:
+                lw["shift"] = vec(w(i, "shift", (D,)))
             m = lc.mixer
-            if not isinstance(m, MinGRUConfig):
+            if not isinstance(m, (MinGRUConfig, MLSTMConfig)):
                 inv_freq, mag = rotary_table(m.rot)
                 lw["inv_freq"], lw["rot_mag"] = inv_freq.to(dev), mag
-            if isinstance(m, MinGRUConfig):
+            if isinstance(m, MLSTMConfig):
+                hd, hv = m.heads * m.dim, m.heads * m.vdim
+                lw["w_proj"] = mat(torch.cat([w(i, "mix.q", (hd, D)), w(i, "mix.k", (hd, D)), w(i, "mix.v", (hv, D)), w(i, "mix.g", (hv, D)),
+                                              w(i, "mix.i", (m.heads, D)), w(i, "mix.f", (m.heads, D))], 0))
+                lw["i_bias"], lw["f_bias"] = vec(w(i, "mix.i.b", (m.heads,))), vec(w(i, "mix.f.b", (m.heads,)))
+                lw["out_gain"] = vec(w(i, "mix.norm", (hv,)))
+                lw["w_o"] = mat(w(i, "mix.o", (D, hv)))
+            elif isinstance(m, MinGRUConfig):
                 lw["w_zxg"] = mat(torch.cat([w(i, "mix.z", (m.width, D)), w(i, "mix.x", (m.width, D)), w(i, "mix.g", (m.width, D))], 0))
                 lw["z_bias"], lw["x_bias"] = vec(w(i, "mix.z.b", (m.width,))), vec(w(i, "mix.x.b", (m.width,)))
                 lw["w_o"] = mat(w(i, "mix.o", (D, m.width)))
             elif isinstance(m, WindowAttentionConfig):
                 if m.heads % m.kv_heads:
                     raise ValueError(f"layer {i}: {m.heads} query heads over {m.kv_heads} key / value heads")
-                lw["w_qkv"] = mat(torch.cat([w(i, "mix.q", (m.heads * m.dim, D)), w(i, "mix.k", (m.kv_heads * m.dim, D)),
-                                             w(i, "mix.v", (m.kv_heads * m.vdim, D))], 0))
+                parts = [w(i, "mix.q", (m.heads * m.dim, D)), w(i, "mix.k", (m.kv_heads * m.dim, D)), w(i, "mix.v", (m.kv_heads * m.vdim, D))]
+                if m.out_gate:
+                    parts.append(w(i, "mix.g", (m.heads * m.vdim, D)))
+                lw["w_qkv"] = mat(torch.cat(parts, 0))
+                if m.bias:
+                    lw["q_bias"], lw["k_bias"] = vec(w(i, "mix.q.b", (m.heads * m.dim,))), vec(w(i, "mix.k.b", (m.kv_heads * m.dim,)))
+                    lw["v_bias"] = vec(w(i, "mix.v.b", (m.kv_heads * m.vdim,)))
+                if m.talking_heads:
+                    lw["talk"] = vec(w(i, "mix.talk", (m.heads, m.heads)))
+                elif m.out_gate:      # the gate rides on the mixing kernel: no mixing is the unit matrix
+                    lw["talk"] = torch.eye(m.heads, dtype=F32).to(dev)
+                if (m.talking_heads or m.out_gate) and m.value_rot is not None:
+                    raise ValueError(f"layer {i}: mixed or gated heads with rotated values are not supported")
                 if m.qk_norm == "head":
                     lw["q_gain"], lw["k_gain"] = vec(w(i, "mix.q.norm", (m.dim,))), vec(w(i, "mix.k.norm", (m.dim,)))
                 elif m.qk_norm == "full":
                     lw["q_gain"] = vec(w(i, "mix.q.norm", (m.heads * m.dim,)))
                     lw["k_gain"] = vec(w(i, "mix.k.norm", (m.kv_heads * m.dim,)))
-                elif m.qk_norm != "none":
+                elif m.qk_norm not in ("none", "unit"):
                     raise ValueError(f"layer {i}: unknown query / key norm {m.qk_norm!r}")
                 if m.value_rot is not None:
                     lw["v_inv_freq"] = rotary_table(m.value_rot)[0].to(dev)
@@ -249,7 +317,17 @@ class SeqLMWeights:
                 lw["decay"] = torch.tensor(m.decay, dtype=torch.float64).to(F32).to(dev)
             else:
                 per = m.dim + m.rot_dim
-                lw["w_qdkv"] = mat(torch.cat([w(i, "mix.q", (m.heads * per, D)), w(i, "mix.dkv", (m.kv_rank + m.rot_dim, D))], 0))
+                # one product of h: [queries or their latent | key / value latent (+ shared rotated key) | one gate per head]
+                parts = [w(i, "mix.dq", (m.q_rank, D)) if m.q_rank else w(i, "mix.q", (m.heads * per, D)),
+                         w(i, "mix.dkv", (m.kv_rank + m.rot_dim, D))]
+                if m.head_gate:
+                    parts.append(w(i, "mix.g", (m.heads, D)))
+                lw["w_qdkv"] = mat(torch.cat(parts, 0))
+                if m.q_rank:
+                    lw["cq_gain"] = vec(w(i, "mix.dq.norm", (m.q_rank,)))
+                    lw["w_uq"] = mat(w(i, "mix.uq", (m.heads * per, m.q_rank)))
+                if m.sink:
+                    lw["sink"] = vec(w(i, "mix.sink", (m.heads,)))
                 lw["c_gain"] = w(i, "mix.dkv.norm", (m.kv_rank,)).float().contiguous().to(dev)
                 uk = w(i, "mix.uk", (m.heads * m.dim, m.kv_rank))
                 lw["w_ukT"] = mat(uk.reshape(m.heads, m.dim, m.kv_rank).transpose(1, 2))       # [heads][kv_rank, dim]
@@ -257,7 +335,8 @@ class SeqLMWeights:
                 lw["w_o"] = mat(w(i, "mix.o", (D, m.heads * m.vdim)))
             f = lc.ff
             if f is not None:
-                lw.update({"norm2": one_plus(i, "norm2")} if pre else {k: num(i, k) for k in ("norm2", "norm2b")})
+                lw.update({"norm2": one_plus(i, "norm2")} if pre else
+                          {k: (one_plus(i, k) if vector else num(i, k)) for k in ("norm2", "norm2b")})
             if isinstance(f, DenseFFConfig):
                 lw["w_up"] = mat(w(i, "mlp.up", (f.ff, D)))
                 lw["w_down"] = mat(w(i, "mlp.down", (D, f.ff)))
@@ -268,11 +347,18 @@ class SeqLMWeights:
                     raise ValueError(f"layer {i}: unknown activation {f.act!r}")
             elif isinstance(f, MoEConfig):
                 lw["w_router"] = mat(w(i, "mlp.router", (f.experts, D)))
-                try:
-                    corr = w(i, "mlp.correction", (f.experts,)).float()
-                except KeyError:                     # a router without a choice bias
-                    corr = torch.zeros(f.experts)
-                lw["correction"] = corr.contiguous().to(dev)
+                if f.router == "softmax_top":
+                    if f.shared_ff or f.n_groups != 1:
+                        raise ValueError(f"layer {i}: the softmax router has neither groups nor a shared expert")
+                    lw["router_bias"] = vec(w(i, "mlp.router.b", (f.experts,)))
+                elif f.router != "grouped_sigmoid":
+                    raise ValueError(f"layer {i}: unknown router {f.router!r}")
+                else:
+                    try:
+                        corr = w(i, "mlp.correction", (f.experts,)).float()
+                    except KeyError:                     # a router without a choice bias
+                        corr = torch.zeros(f.experts)
+                    lw["correction"] = corr.contiguous().to(dev)
                 gu = [torch.cat([w(i, f"mlp.e{e}.gate", (f.expert_ff, D)), w(i, f"mlp.e{e}.up", (f.expert_ff, D))], 0)
                       for e in range(f.experts)]
                 lw["w_gu"] = mat(torch.stack(gu, 0))                                           # [experts][2 ff, D]
@@ -398,10 +484,13 @@ class SeqLMEngine:
         self.act = BF16 if dtype == "bfloat16" else F32
         # what every layer keeps per request: rows of a paged cache (attention), rows of a summary pool (pooled blocks), a state
         rows, states, summaries, looks, keep = [], [], [], [], 0
-        self._cache_index, self._state_index, self._summary_index = [], [], []
+        self._cache_index, self._state_index, self._summary_index, self._shift_index = [], [], [], []
         for lc in cfg.layers:
             m = lc.mixer
             ci = si = pi = -1
+            self._shift_index.append(len(states) if lc.token_shift else -1)
+            if lc.token_shift:
+                states.append((cfg.width,))
             if isinstance(m, LatentAttentionConfig):
                 ci = len(rows)
                 rows.append(m.kv_rank + m.rot_dim)
@@ -422,6 +511,9 @@ class SeqLMEngine:
             elif isinstance(m, MinGRUConfig):
                 si = len(states)
                 states.append((m.width,))
+            elif isinstance(m, MLSTMConfig):
+                si = len(states)
+                states.append((m.heads, m.dim + 1, m.vdim + 1))      # per head S | n, and the running maximum in the last row
             else:
                 raise TypeError(f"unknown mixer {type(m).__name__}")
             self._cache_index.append(ci)
@@ -540,14 +632,21 @@ class SeqLMEngine:
     def _latent(self, li: int, m: LatentAttentionConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
         per = m.dim + m.rot_dim
         qd = self.linear(h, lw["w_qdkv"], F32)
-        q, dkv = qd[:, : m.heads * per], qd[:, m.heads * per:]
+        nq = m.q_rank or m.heads * per
+        dkv = qd[:, nq: nq + m.kv_rank + m.rot_dim]
+        gate = qd[:, nq + m.kv_rank + m.rot_dim:] if m.head_gate else None
+        if m.q_rank:      # queries through their own normed latent
+            q = self.linear(self.norm(qd[:, :nq], lw["cq_gain"], self.act), lw["w_uq"], F32)
+        else:
+            q = qd[:, :nq]
         pool = self.cache.pools[self._cache_index[li]]
-        d = _lib.LatentDesc(q=_lib.ptr(q), ldq=qd.stride(0), dkv=_lib.ptr(dkv), lddkv=qd.stride(0), heads=m.heads, dim=m.dim,
+        d = _lib.LatentDesc(q=_lib.ptr(q), ldq=q.stride(0), dkv=_lib.ptr(dkv), lddkv=qd.stride(0), heads=m.heads, dim=m.dim,
                             rot_dim=m.rot_dim, kv_rank=m.kv_rank, c_gain=_lib.ptr(lw["c_gain"]), eps=self.cfg.eps,
                             inv_freq=_lib.ptr(lw["inv_freq"]), rot_dims=m.rot.dims,
                             rot_layout=_lib.ROT_INTERLEAVED if m.rot.layout == "interleaved" else _lib.ROT_HALF,
                             rot_mscale=lw["rot_mag"], cache=_lib.ptr(pool), page_size=self.cache.page_size,
-                            page_table=_lib.ptr(b.page_table), max_pages=b.max_pages, window=m.window or 0, scale=m.scale)
+                            page_table=_lib.ptr(b.page_table), max_pages=b.max_pages, window=m.window or 0, scale=m.scale,
+                            sink=_lib.ptr(lw.get("sink")), gate=_lib.ptr(gate), ldg=qd.stride(0) if gate is not None else 0)
         self._check(self.L.lp_latent_prep(C.byref(d), b.R, _lib.ptr(b.row_seq), _lib.ptr(b.row_pos), self._stream()), "lp_latent_prep")
         q_abs = self._empty((b.R, m.heads * m.kv_rank), F32)
         self.linear_heads(q, per, lw["w_ukT"], q_abs, m.kv_rank)
@@ -569,9 +668,13 @@ class SeqLMEngine:
         stream = cache.summary_index[pi][0] if pi >= 0 else -1
         layouts = {"half": _lib.ROT_HALF, "interleaved": _lib.ROT_INTERLEAVED}
         vr = m.value_rot
+        mixing = m.talking_heads or m.out_gate
         d = _lib.WindowAttnDesc(
             qkv=_lib.ptr(qkv), ld=qkv.stride(0), q_off=0, k_off=hq, v_off=hq + hk, heads=m.heads, kv_heads=m.kv_heads, dim=m.dim,
-            vdim=m.vdim, norm_mode={"none": _lib.QKNORM_NONE, "head": _lib.QKNORM_HEAD, "full": _lib.QKNORM_FULL}[m.qk_norm],
+            vdim=m.vdim,
+            norm_mode={"none": _lib.QKNORM_NONE, "head": _lib.QKNORM_HEAD, "unit": _lib.QKNORM_HEAD, "full": _lib.QKNORM_FULL}[m.qk_norm],
+            q_bias=_lib.ptr(lw.get("q_bias")), k_bias=_lib.ptr(lw.get("k_bias")), v_bias=_lib.ptr(lw.get("v_bias")),
+            v_norm=int(m.value_norm), talk=_lib.ptr(lw.get("talk")), g_off=hq + hk + m.kv_heads * m.vdim if m.out_gate else -1,
             q_gain=_lib.ptr(lw.get("q_gain")), k_gain=_lib.ptr(lw.get("k_gain")), eps=self.cfg.eps, inv_freq=_lib.ptr(lw["inv_freq"]),
             rot_dims=m.rot.dims, rot_layout=layouts[m.rot.layout], rot_mscale=lw["rot_mag"],
             v_inv_freq=_lib.ptr(lw.get("v_inv_freq")), v_rot_dims=vr.dims if vr else 0, v_rot_layout=layouts[vr.layout] if vr else 0,
@@ -589,7 +692,10 @@ class SeqLMEngine:
             rc = self.L.lp_window_attn_pool(C.byref(d), b.n, _lib.ptr(b.seq_row0), _lib.ptr(b.seq_pos0), new, st)
             self._check(rc, "lp_window_attn_pool")
         o = self._empty((b.R, m.heads * m.vdim), self.act)
-        if b.decode:
+        if mixing:      # weights mixed over the heads (and the output gate): one kernel for prompts and one-token steps
+            rc = self.L.lp_window_attn_talk(C.byref(d), b.R, _lib.ptr(b.row_seq), _lib.ptr(b.row_pos), _lib.ptr(o), o.stride(0),
+                                            int(o.dtype == F32), st)
+        elif b.decode:
             rc = self.L.lp_window_attn(C.byref(d), b.R, _lib.ptr(b.row_seq), _lib.ptr(b.row_pos), _lib.ptr(o), o.stride(0),
                                        int(o.dtype == F32), st)
         else:      # prompts and portions: tiles of consecutive rows share the keys they read
@@ -617,7 +723,26 @@ class SeqLMEngine:
             self._check(rc, "lp_mingru_prefill")
         return self.linear(out, lw["w_o"], F32, into=into)
 
+    def _mlstm(self, li: int, m: MLSTMConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
+        proj = self.linear(h, lw["w_proj"], F32)
+        hd, hv = m.heads * m.dim, m.heads * m.vdim
+        out = self._empty((b.R, hv), self.act)
+        state = self.cache.states[self._state_index[li]]
+        d = _lib.MLSTMDesc(proj=_lib.ptr(proj), ld=proj.stride(0), q_off=0, k_off=hd, v_off=2 * hd, g_off=2 * hd + hv,
+                           i_off=2 * hd + 2 * hv, f_off=2 * hd + 2 * hv + m.heads, heads=m.heads, dim=m.dim, vdim=m.vdim,
+                           i_bias=_lib.ptr(lw["i_bias"]), f_bias=_lib.ptr(lw["f_bias"]), gate_cap=m.gate_cap, q_scale=m.dim ** -0.5,
+                           eps=self.cfg.eps, out_gain=_lib.ptr(lw["out_gain"]), state=_lib.ptr(state), slot_stride=state.stride(0),
+                           out=_lib.ptr(out), ldo=out.stride(0), out_fp32=int(out.dtype == F32))
+        nbytes = int(self.L.lp_mlstm_workspace_bytes(b.R, m.heads, m.vdim))
+        ws = self._empty((nbytes // 4,), F32)
+        rc = self.L.lp_mlstm(C.byref(d), b.n, b.R, _lib.ptr(b.seq_row0), _lib.ptr(b.seq_pos0), _lib.ptr(b.seq_slot), _lib.ptr(ws), nbytes,
+                             self._stream())
+        self._check(rc, "lp_mlstm")
+        return self.linear(out, lw["w_o"], F32, into=into)
+
     def _mix(self, li: int, m, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
+        if isinstance(m, MLSTMConfig):
+            return self._mlstm(li, m, lw, h, b, into)
         if isinstance(m, RetentionConfig):
             return self._retention(li, m, lw, h, b, into)
         if isinstance(m, LatentAttentionConfig):
@@ -640,9 +765,14 @@ class SeqLMEngine:
         idx = self._empty((T, f.top), I32)
         wts = self._empty((T, f.top), F32)
         gate = self._empty((T,), F32) if f.shared_ff else None
-        rc = L.lp_moe_route(_lib.ptr(h), h.stride(0), int(h.dtype == F32), T, D, _lib.ptr(lw["w_router"]), lw["w_router"].stride(0),
-                            f.experts, _lib.ptr(lw["correction"]), f.n_groups, f.keep_groups, f.top,
-                            _lib.ptr(lw["w_sg"]) if f.shared_ff else None, _lib.ptr(idx), _lib.ptr(wts), _lib.ptr(gate), st)
+        if f.router == "softmax_top":
+            rc = L.lp_moe_route_softmax(_lib.ptr(h), h.stride(0), int(h.dtype == F32), T, D, _lib.ptr(lw["w_router"]),
+                                        lw["w_router"].stride(0), f.experts, _lib.ptr(lw["router_bias"]), f.top, _lib.ptr(idx),
+                                        _lib.ptr(wts), st)
+        else:
+            rc = L.lp_moe_route(_lib.ptr(h), h.stride(0), int(h.dtype == F32), T, D, _lib.ptr(lw["w_router"]), lw["w_router"].stride(0),
+                                f.experts, _lib.ptr(lw["correction"]), f.n_groups, f.keep_groups, f.top,
+                                _lib.ptr(lw["w_sg"]) if f.shared_ff else None, _lib.ptr(idx), _lib.ptr(wts), _lib.ptr(gate), st)
         self._check(rc, "lp_moe_route")
         n_pairs = T * f.top
         if n_pairs <= MOE_PAIRS_MAX:
@@ -764,9 +894,25 @@ class SeqLMEngine:
         rc = self.L.lp_embed_rows_f32(_lib.ptr(b.tokens), b.R, _lib.ptr(self.w.embed), self.w.embed.stride(0), cfg.vocab, cfg.embed_scale,
                                       _lib.ptr(x), x.stride(0), D, self._stream())
         self._check(rc, "lp_embed_rows_f32")
+        if cfg.position_base > 0:
+            rc = self.L.lp_add_positions_f32(_lib.ptr(x), x.stride(0), b.R, D, _lib.ptr(b.row_pos), _lib.ptr(self.w.position_freq),
+                                             self._stream())
+            self._check(rc, "lp_add_positions_f32")
         pre = cfg.norm == "pre"
         for li, (lc, lw) in enumerate(zip(cfg.layers, self.w.layers)):
-            h = self.norm(x, lw["norm1"], self.act)
+            if self.w.add_before[li] is not None:
+                rc = self.L.lp_add_row_f32(_lib.ptr(x), x.stride(0), _lib.ptr(self.w.add_before[li]), b.R, D, self._stream())
+                self._check(rc, "lp_add_row_f32")
+            if lc.token_shift:      # the normed stream in fp32, then shifted towards the previous token's into the operand dtype
+                hn = self.norm(x, lw["norm1"], F32)
+                h = self._empty((b.R, D), self.act)
+                state = self.cache.states[self._shift_index[li]]
+                rc = self.L.lp_token_shift_f32(_lib.ptr(hn), hn.stride(0), _lib.ptr(lw["shift"]), b.R, D, _lib.ptr(b.row_seq),
+                                               _lib.ptr(b.row_pos), _lib.ptr(b.seq_row0), _lib.ptr(b.seq_slot), _lib.ptr(state),
+                                               state.stride(0), _lib.ptr(h), h.stride(0), int(h.dtype == F32), self._stream())
+                self._check(rc, "lp_token_shift_f32")
+            else:
+                h = self.norm(x, lw["norm1"], self.act)
             if pre:        # x <- x + m * mixer(norm(x)): the update is the store of the mixer's output product
                 self._mix(li, lc.mixer, lw, h, b, into=(x, cfg.residual_mult))
             else:

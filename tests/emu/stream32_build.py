@@ -1,4 +1,4 @@
-"""Test infrastructure: builds the 32-bit residual-stream kernel files (lp_linear.cu, lp_stream32.cu, lp_seqmix.cu, lp_winattn.cu, lp_mingru.cu, lp_moe.cu — kernels
+"""Test infrastructure: builds the 32-bit residual-stream kernel files (lp_linear.cu, lp_stream32.cu, lp_seqmix.cu, lp_winattn.cu, lp_mingru.cu, lp_mlstm.cu, lp_moe.cu — kernels
 AND their host entry points) for the CPU emulator: includes dropped, dynamic shared memory turned into a static buffer, launches
 rewritten (launch_rewrite.py), runtime names from host_emu.h.  The result exports the same C symbols as the native library."""
 import subprocess
@@ -6,7 +6,7 @@ import sys
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parents[2]
-SOURCES = ("lp_linear", "lp_stream32", "lp_seqmix", "lp_winattn", "lp_mingru", "lp_moe")
+SOURCES = ("lp_linear", "lp_stream32", "lp_seqmix", "lp_winattn", "lp_mingru", "lp_mlstm", "lp_moe")
 
 
 def build_emulated(out: Path) -> Path:
