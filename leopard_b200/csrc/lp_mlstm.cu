@@ -12,11 +12,11 @@
 //
 //   lp_mlstm   two kernels for prompts, portions and one-token steps alike:
 //     scan     a CTA per (request, head, tile of 32 state columns); the normaliser n is one more COLUMN of the state (its "value" is
-//              1), so S and n share the code.  A thread owns 32 rows of one column in registers (threadIdx.y picks the rows when dim
-//              exceeds 32).  Tokens are staged in shared memory 16 at a time: the gate transforms of the 16 tokens in parallel, the
-//              running maximum by one thread (two adds and a max per token), the two exponentials per token in parallel, then the
-//              16 state updates without any synchronisation; the partial read-outs of the row groups meet in shared memory once per
-//              16 tokens.  The state is read from and written to the request's slot ([dim + 1][vdim + 1] per head: S | n, and m
+//              1), so S and n share the code.  A thread owns 16 rows of one column in registers (threadIdx.y picks the rows when dim
+//              exceeds 16).  Tokens are staged in shared memory 16 at a time, the next stage travelling from global memory into
+//              registers meanwhile: the gate transforms of the 16 tokens in parallel, the running maximum by one thread (an add and
+//              a max per token), the two exponentials per token in parallel, then the 16 state updates without any
+//              synchronisation; the partial read-outs of the row groups meet in shared memory once per 16 tokens.  The state is read from and written to the request's slot ([dim + 1][vdim + 1] per head: S | n, and m
 //              in the last row, one copy per column tile) — a request at position 0 starts from zero without reading it.
 //     finish   a warp per (row, head): denominator, unit RMS, gain, gate.
 // The recurrence is run token by token in every case, so a row's result does not depend on how the tokens were cut into steps.
@@ -38,16 +38,18 @@ struct MlstmArgs {
 };
 
 constexpr int MLSTM_COLS = 32;      // state columns per CTA
-constexpr int MLSTM_ROWS = 32;      // state rows per thread
+constexpr int MLSTM_ROWS = 16;      // state rows per thread
 constexpr int MLSTM_TOK = 16;       // tokens staged at a time
+constexpr int MLSTM_MAX_GROUPS = 16;      // row groups (threadIdx.y) per CTA: dim <= 256
 
 __device__ __forceinline__ float mlstm_logsigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
 // num [rows][heads][vdim + 1] (the last column is n . q), mrow [rows][heads]
-__global__ void __launch_bounds__(MLSTM_COLS * 8)
+__global__ void __launch_bounds__(MLSTM_COLS * MLSTM_MAX_GROUPS)
 mlstm_scan_kernel(MlstmArgs a, const int* __restrict__ seq_row0, const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot,
                   float* __restrict__ num, float* __restrict__ mrow) {
   extern __shared__ float dyn_smem[];
+  constexpr int PF = MLSTM_TOK * MLSTM_ROWS / MLSTM_COLS;      // q (and k) elements a thread brings per stage
   const int s = blockIdx.x, h = blockIdx.y;
   const int tx = threadIdx.x, ty = threadIdx.y, NS = blockDim.y;
   const int tid = ty * MLSTM_COLS + tx, nthreads = MLSTM_COLS * NS;
@@ -55,10 +57,10 @@ mlstm_scan_kernel(MlstmArgs a, const int* __restrict__ seq_row0, const int* __re
   float* q_s = dyn_smem;                            // [TOK][dpad], zero beyond dim
   float* k_s = q_s + MLSTM_TOK * dpad;              // [TOK][dpad]
   float* v_s = k_s + MLSTM_TOK * dpad;              // [TOK][COLS] the tile's values; 1 for the normaliser column
-  float* gi_s = v_s + MLSTM_TOK * MLSTM_COLS;       // [TOK] log input gates, then exp(i - m_t)
+  float* red_s = v_s + MLSTM_TOK * MLSTM_COLS;      // [TOK][NS][COLS] partial read-outs
+  float* gi_s = red_s + MLSTM_TOK * NS * MLSTM_COLS;      // [TOK] log input gates, then exp(i - m_t)
   float* gf_s = gi_s + MLSTM_TOK;                   // [TOK] log forget gates, then exp(f + m_(t-1) - m_t)
-  float* m_s = gf_s + MLSTM_TOK;                    // [TOK + 1] m before the chunk, then after each token
-  float* red_s = m_s + MLSTM_TOK + 1;               // [TOK][NS][COLS] partial read-outs
+  float* m_s = gf_s + MLSTM_TOK;                    // [TOK + 1] m before the stage, then after each token
   const int row0 = seq_row0[s], len = seq_row0[s + 1] - row0, pos0 = seq_pos0[s];
   const int col = blockIdx.z * MLSTM_COLS + tx;     // 0 .. vdim (vdim: the normaliser)
   const bool live = col <= a.vdim;
@@ -73,30 +75,65 @@ mlstm_scan_kernel(MlstmArgs a, const int* __restrict__ seq_row0, const int* __re
   // every column tile keeps its own copy of m in the state's last row (at its first column): no CTA reads what another one writes
   float* m_slot = slot + (long long)a.dim * cols + blockIdx.z * MLSTM_COLS;
   if (tid == 0) m_s[0] = pos0 > 0 ? *m_slot : 0.f;
+  // the next stage's operands travel from global memory into registers while the current stage computes
+  float pq[PF], pk[PF], pv[MLSTM_TOK / 2], pgi = 0.f, pgf = 0.f;      // at least two row groups: 8 tokens' values each at most
+  auto fetch = [&](int c0) {
+    const int nt = len - c0 < MLSTM_TOK ? len - c0 : MLSTM_TOK;
+#pragma unroll
+    for (int j = 0; j < PF; ++j) {
+      const int i = tid + j * nthreads, t = i / dpad, d = i % dpad;
+      const bool ok = t < nt && d < a.dim;
+      const float* row = a.proj + (long long)(row0 + c0 + (ok ? t : 0)) * a.ld + h * a.dim + (ok ? d : 0);
+      pq[j] = ok ? row[a.q_off] * a.q_scale : 0.f;
+      pk[j] = ok ? row[a.k_off] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < MLSTM_TOK / 2; ++j) {      // thread (tx, ty) brings column tx of tokens ty, ty + NS, ...
+      const int t = ty + j * NS;
+      if (t < MLSTM_TOK) {
+        const bool ok = t < nt && col < a.vdim;
+        pv[j] = ok ? a.proj[(long long)(row0 + c0 + t) * a.ld + a.v_off + h * a.vdim + col] : (col == a.vdim ? 1.f : 0.f);
+      }
+    }
+    if (tid < MLSTM_TOK) {
+      const bool ok = tid < nt;
+      const float* row = a.proj + (long long)(row0 + c0 + (ok ? tid : 0)) * a.ld;
+      pgi = ok ? row[a.i_off + h] + a.i_bias[h] : 0.f;
+      pgf = ok ? row[a.f_off + h] + a.f_bias[h] : 0.f;
+    }
+  };
+  fetch(0);
   for (int c0 = 0; c0 < len; c0 += MLSTM_TOK) {
     const int nt = len - c0 < MLSTM_TOK ? len - c0 : MLSTM_TOK;
-    __syncthreads();      // the previous chunk has been read
-    for (int i = tid; i < nt * dpad; i += nthreads) {
-      const int t = i / dpad, d = i % dpad;
-      const float* row = a.proj + (long long)(row0 + c0 + t) * a.ld;
-      q_s[i] = d < a.dim ? row[a.q_off + h * a.dim + d] * a.q_scale : 0.f;
-      k_s[i] = d < a.dim ? row[a.k_off + h * a.dim + d] : 0.f;
+    __syncthreads();      // the previous stage has been read
+#pragma unroll
+    for (int j = 0; j < PF; ++j) {
+      q_s[tid + j * nthreads] = pq[j];
+      k_s[tid + j * nthreads] = pk[j];
     }
-    for (int i = tid; i < nt * MLSTM_COLS; i += nthreads) {
-      const int t = i / MLSTM_COLS, c = blockIdx.z * MLSTM_COLS + i % MLSTM_COLS;
-      const float* row = a.proj + (long long)(row0 + c0 + t) * a.ld;
-      v_s[i] = c < a.vdim ? row[a.v_off + h * a.vdim + c] : (c == a.vdim ? 1.f : 0.f);
+#pragma unroll
+    for (int j = 0; j < MLSTM_TOK / 2; ++j) {
+      const int t = ty + j * NS;
+      if (t < MLSTM_TOK) v_s[t * MLSTM_COLS + tx] = pv[j];
     }
-    if (tid < nt) {
-      const float* row = a.proj + (long long)(row0 + c0 + tid) * a.ld;
-      gi_s[tid] = a.gate_cap * tanhf((row[a.i_off + h] + a.i_bias[h]) / a.gate_cap);
-      gf_s[tid] = mlstm_logsigmoid(a.gate_cap * tanhf((row[a.f_off + h] + a.f_bias[h]) / a.gate_cap));
+    if (tid < MLSTM_TOK) {
+      // tokens past the end of the request leave m as it is: max(0 + m, -inf)
+      gi_s[tid] = tid < nt ? a.gate_cap * tanhf(pgi / a.gate_cap) : -INFINITY;
+      gf_s[tid] = tid < nt ? mlstm_logsigmoid(a.gate_cap * tanhf(pgf / a.gate_cap)) : 0.f;
     }
     __syncthreads();
-    if (tid == 0) {
+    if (c0 + MLSTM_TOK < len) fetch(c0 + MLSTM_TOK);
+    if (tid == 0) {      // the running maximum: an add and a max per token, everything in registers
+      float gi[MLSTM_TOK], gf[MLSTM_TOK];
+#pragma unroll
+      for (int t = 0; t < MLSTM_TOK; ++t) {
+        gi[t] = gi_s[t];
+        gf[t] = gf_s[t];
+      }
       float m = m_s[0];
-      for (int t = 0; t < nt; ++t) {
-        m = fmaxf(gf_s[t] + m, gi_s[t]);
+#pragma unroll
+      for (int t = 0; t < MLSTM_TOK; ++t) {
+        m = fmaxf(gf[t] + m, gi[t]);
         m_s[t + 1] = m;
       }
     }
@@ -108,51 +145,38 @@ mlstm_scan_kernel(MlstmArgs a, const int* __restrict__ seq_row0, const int* __re
       if (blockIdx.z == 0) mrow[(long long)(row0 + c0 + tid) * a.heads + h] = m_s[tid + 1];
     }
     __syncthreads();
-    float acc[MLSTM_TOK];
+#pragma unroll 2
+    for (int t = 0; t < nt; ++t) {
+      const float keep = gf_s[t], kv = gi_s[t] * v_s[t * MLSTM_COLS + tx];
+      const float* kq = k_s + t * dpad + ty * MLSTM_ROWS;
+      const float* qq = q_s + t * dpad + ty * MLSTM_ROWS;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-    for (int t = 0; t < MLSTM_TOK; ++t) {
-      acc[t] = 0.f;
-      if (t < nt) {
-        const float keep = gf_s[t], kv = gi_s[t] * v_s[t * MLSTM_COLS + tx];
-        const float* kq = k_s + t * dpad + ty * MLSTM_ROWS;
-        const float* qq = q_s + t * dpad + ty * MLSTM_ROWS;
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-        for (int dd = 0; dd < MLSTM_ROWS; dd += 4) {
-          const float4 k4 = *reinterpret_cast<const float4*>(kq + dd);
-          const float4 q4 = *reinterpret_cast<const float4*>(qq + dd);
-          S[dd] = fmaf(keep, S[dd], k4.x * kv);
-          S[dd + 1] = fmaf(keep, S[dd + 1], k4.y * kv);
-          S[dd + 2] = fmaf(keep, S[dd + 2], k4.z * kv);
-          S[dd + 3] = fmaf(keep, S[dd + 3], k4.w * kv);
-          a0 = fmaf(S[dd], q4.x, a0);
-          a1 = fmaf(S[dd + 1], q4.y, a1);
-          a2 = fmaf(S[dd + 2], q4.z, a2);
-          a3 = fmaf(S[dd + 3], q4.w, a3);
-        }
-        acc[t] = (a0 + a1) + (a2 + a3);
+      for (int dd = 0; dd < MLSTM_ROWS; dd += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kq + dd);
+        const float4 q4 = *reinterpret_cast<const float4*>(qq + dd);
+        S[dd] = fmaf(keep, S[dd], k4.x * kv);
+        S[dd + 1] = fmaf(keep, S[dd + 1], k4.y * kv);
+        S[dd + 2] = fmaf(keep, S[dd + 2], k4.z * kv);
+        S[dd + 3] = fmaf(keep, S[dd + 3], k4.w * kv);
+        a0 = fmaf(S[dd], q4.x, a0);
+        a1 = fmaf(S[dd + 1], q4.y, a1);
+        a2 = fmaf(S[dd + 2], q4.z, a2);
+        a3 = fmaf(S[dd + 3], q4.w, a3);
+      }
+      red_s[(t * NS + ty) * MLSTM_COLS + tx] = (a0 + a1) + (a2 + a3);
+    }
+    __syncthreads();
+    for (int i = tid; i < nt * MLSTM_COLS; i += nthreads) {      // the row groups' partial read-outs, summed in their order
+      const int t = i / MLSTM_COLS, c = i % MLSTM_COLS;
+      const int cc = blockIdx.z * MLSTM_COLS + c;
+      if (cc <= a.vdim) {
+        float v = 0.f;
+        for (int y = 0; y < NS; ++y) v += red_s[(t * NS + y) * MLSTM_COLS + c];
+        num[((long long)(row0 + c0 + t) * a.heads + h) * cols + cc] = v;
       }
     }
-    if (NS > 1) {
-#pragma unroll
-      for (int t = 0; t < MLSTM_TOK; ++t)
-        if (t < nt) red_s[(t * NS + ty) * MLSTM_COLS + tx] = acc[t];
-      __syncthreads();
-      for (int i = tid; i < nt * MLSTM_COLS; i += nthreads) {
-        const int t = i / MLSTM_COLS, c = i % MLSTM_COLS;
-        const int cc = blockIdx.z * MLSTM_COLS + c;
-        if (cc <= a.vdim) {
-          float v = 0.f;
-          for (int y = 0; y < NS; ++y) v += red_s[(t * NS + y) * MLSTM_COLS + c];
-          num[((long long)(row0 + c0 + t) * a.heads + h) * cols + cc] = v;
-        }
-      }
-    } else if (live) {
-#pragma unroll
-      for (int t = 0; t < MLSTM_TOK; ++t)
-        if (t < nt) num[((long long)(row0 + c0 + t) * a.heads + h) * cols + col] = acc[t];
-    }
-    if (tid == 0) m_s[0] = m_s[nt];      // read again only after the next chunk's first barrier
+    if (tid == 0) m_s[0] = m_s[nt];      // read again only after the next stage's barriers
   }
   if (live) {
 #pragma unroll
@@ -206,8 +230,8 @@ extern "C" int lp_mlstm(const lp_mlstm_desc* d, int n_seqs, int R, const int* se
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LP_REQUIRE(d != nullptr && d->proj != nullptr && d->i_bias != nullptr && d->f_bias != nullptr && d->state != nullptr && d->out != nullptr,
              "lp_mlstm: null operand");
-  LP_REQUIRE(d->heads > 0 && d->dim > 0 && d->vdim > 0 && d->dim <= 7 * MLSTM_ROWS, "lp_mlstm: bad sizes heads=%d dim=%d (at most %d) vdim=%d",
-             d->heads, d->dim, 7 * MLSTM_ROWS, d->vdim);
+  LP_REQUIRE(d->heads > 0 && d->dim > 0 && d->vdim > 0 && d->dim <= MLSTM_MAX_GROUPS * MLSTM_ROWS,
+             "lp_mlstm: bad sizes heads=%d dim=%d (at most %d) vdim=%d", d->heads, d->dim, MLSTM_MAX_GROUPS * MLSTM_ROWS, d->vdim);
   LP_REQUIRE(d->gate_cap > 0.f, "lp_mlstm: gate_cap must be positive");
   LP_REQUIRE(d->slot_stride >= (long long)d->heads * (d->dim + 1) * (d->vdim + 1), "lp_mlstm: a slot is smaller than the state");
   LP_REQUIRE(seq_row0 != nullptr && seq_pos0 != nullptr && seq_slot != nullptr && n_seqs >= 0 && R >= 0, "lp_mlstm: bad batch tables");
@@ -220,9 +244,14 @@ extern "C" int lp_mlstm(const lp_mlstm_desc* d, int n_seqs, int R, const int* se
   a.slot_stride = d->slot_stride; a.out = d->out; a.ldo = d->ldo; a.out_fp32 = d->out_fp32;
   float* num = reinterpret_cast<float*>(ws);
   float* mrow = num + (size_t)R * d->heads * (d->vdim + 1);
-  const int ns = (d->dim + MLSTM_ROWS - 1) / MLSTM_ROWS;
-  const size_t smem = ((size_t)2 * MLSTM_TOK * ns * MLSTM_ROWS + MLSTM_TOK * MLSTM_COLS + 3 * MLSTM_TOK + 1 +
-                       (size_t)MLSTM_TOK * ns * MLSTM_COLS + 3) * sizeof(float);      // < 48 kB for every dim allowed
+  const int ns = d->dim <= MLSTM_ROWS ? 2 : (d->dim + MLSTM_ROWS - 1) / MLSTM_ROWS;      // at least two row groups (rows past dim stay zero)
+  const size_t smem = ((size_t)2 * MLSTM_TOK * ns * MLSTM_ROWS + MLSTM_TOK * MLSTM_COLS + (size_t)MLSTM_TOK * ns * MLSTM_COLS +
+                       3 * MLSTM_TOK + 4) * sizeof(float);
+  static size_t have = 48 * 1024;      // raised once, and only for head sizes that need it
+  if (smem > have) {
+    LP_CHECK_CUDA(cudaFuncSetAttribute(mlstm_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    have = 96 * 1024;
+  }
   mlstm_scan_kernel<<<dim3(n_seqs, d->heads, (d->vdim + 1 + MLSTM_COLS - 1) / MLSTM_COLS), dim3(MLSTM_COLS, ns), smem, stream>>>(
       a, seq_row0, seq_pos0, seq_slot, num, mrow);
   LP_CHECK_CUDA(cudaGetLastError());

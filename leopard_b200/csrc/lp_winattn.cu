@@ -21,7 +21,7 @@
 //                         time), the warp agrees on the running maximum, then the 32 values are accumulated with the
 //                         lanes spread over vdim (weights and row addresses broadcast through shared memory).  The CTA's warps take every W-th tile
 //                         and merge their (maximum, denominator, sum) triples at the end.  All of it in fp32.
-//   lp_window_attn_talk   one CTA per row and ALL heads, two passes over the visible keys in tiles of 64: the first finds every head's
+//   lp_window_attn_talk   one CTA per row and ALL heads, two passes over the visible keys in tiles: the first finds every head's
 //                         softmax maximum and denominator, the second computes the scores again, normalises them, mixes them over
 //                         the heads in shared memory and adds the values with the mixed weights.
 //   lp_window_attn_tiles  the same for prompts, a CTA per tile of 2 or 4 consecutive rows of a request: the rows share every key and
@@ -667,20 +667,19 @@ window_attn_tile_kernel(WinArgs a, int n_chunks, const int* __restrict__ chunk_s
 // Talking heads: the softmax weights of all heads are mixed, weight_h(i, j) <- sum_g talk[h, g] weight_g(i, j), before head h applies
 // them to the values of its own key / value head — so a row needs the NORMALISED weights of every head at every key.  One CTA per
 // row and all heads; the visible keys (the same index space as above: kept tokens, pooled blocks, window) are walked twice in tiles
-// of TALK_TILE keys.  Pass 1: scores of the tile for every head -> running maximum and denominator per head.  Pass 2: the same
+// of 64 to 256 keys.  Pass 1: scores of the tile for every head -> running maximum and denominator per head.  Pass 2: the same
 // scores again (the same arithmetic, so the same numbers), weights = exp(score - max) / denominator, mixed over the heads in shared
 // memory, then every thread adds the tile's values to the (head, value channel) sums it owns.  Nothing is rescaled in pass 2: the
 // weights are final.  An output gate, when the description names one, multiplies the sums by sigmoid(g) on the way out.
-constexpr int TALK_TILE = 64;
-constexpr int TALK_THREADS = 256;
-constexpr int TALK_MAX_ACC = 32;      // heads * vdim <= TALK_THREADS * TALK_MAX_ACC
+constexpr int TALK_MAX_ACC = 32;      // heads * vdim <= 256 * TALK_MAX_ACC
 
 // scores of one tile -> p_s[h][jj] (scaled and capped); a thread takes one key and up to four query heads of one key / value head
-__device__ __forceinline__ void talk_tile_scores(const WinArgs& a, const WinVisible& vis, int seq, int t0, int cnt, const float* q_s,
+__device__ __forceinline__ void talk_tile_scores(const WinArgs& a, const WinVisible& vis, int seq, int t0, int cnt, int tile, const float* q_s,
                                                  float* p_s, const float** row_s, int tid, int nthreads) {
   const int ratio = a.heads / a.kv_heads;
   const int hgroups = (ratio + 3) / 4;      // groups of at most four query heads per key / value head
-  for (int jj = tid; jj < cnt; jj += nthreads) row_s[jj] = win_visible_row(a, vis, seq, t0 + jj);
+  const int cnt4 = (cnt + 3) & ~3;
+  for (int jj = tid; jj < cnt4; jj += nthreads) row_s[jj] = win_visible_row(a, vis, seq, t0 + (jj < cnt ? jj : 0));
   __syncthreads();
   const bool vec = (a.dim % 4 == 0) && (a.vdim % 4 == 0);
   for (int it = tid; it < a.kv_heads * hgroups * cnt; it += nthreads) {
@@ -716,51 +715,53 @@ __device__ __forceinline__ void talk_tile_scores(const WinArgs& a, const WinVisi
       if (h < nh) {
         float v = sc[h] * a.scale;
         if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
-        p_s[(h0 + h) * TALK_TILE + jj] = v;
+        p_s[(h0 + h) * tile + jj] = v;
       }
     }
   }
   __syncthreads();
 }
 
-template <int NACC>
-__global__ void __launch_bounds__(TALK_THREADS)
-window_attn_talk_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const int* __restrict__ row_pos, void* __restrict__ out,
+// `tile` keys at a time (a multiple of 4, chosen by the host so that a tile's (key, head group) pairs occupy the CTA's threads)
+template <int NACC, int NT>
+__global__ void __launch_bounds__(NT)
+window_attn_talk_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const int* __restrict__ row_pos, int tile, void* __restrict__ out,
                         long long ldo, int out_fp32) {
   extern __shared__ float dyn_smem[];
   const int r = blockIdx.x;
   if (r >= R) return;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthreads = blockDim.x, n_warps = blockDim.x >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr int n_warps = NT / 32;
   const int H = a.heads, ratio = a.heads / a.kv_heads;
-  const float** row_s = reinterpret_cast<const float**>(dyn_smem);      // [TALK_TILE] cache row of each key of the tile
-  float* q_s = dyn_smem + 2 * TALK_TILE;        // [H][dim]
-  float* p_s = q_s + H * a.dim;                 // [H][TALK_TILE] scores, then weights
-  float* w_s = p_s + H * TALK_TILE;             // [H][TALK_TILE] mixed weights
-  float* m_s = w_s + H * TALK_TILE;             // [H] maxima
+  const float** row_s = reinterpret_cast<const float**>(dyn_smem);      // [tile] cache row of each key of the tile
+  float* q_s = dyn_smem + 2 * tile;             // [H][dim]
+  float* p_s = q_s + ((H * a.dim + 3) & ~3);    // [H][tile] scores, then weights
+  float* w_s = p_s + H * tile;                  // [H][tile] mixed weights
+  float* m_s = w_s + H * tile;                  // [H] maxima
   float* l_s = m_s + H;                         // [H] denominators, then their inverses
   float* t_s = l_s + H;                         // [H][H] the mixing matrix
   const int seq = row_seq[r], pos = row_pos[r];
   const float* q = a.qkv + (long long)r * a.ld + a.q_off;
-  for (int i = tid; i < H * a.dim; i += nthreads) q_s[i] = q[i];
-  for (int i = tid; i < H * H; i += nthreads) t_s[i] = a.talk[i];
-  for (int h = tid; h < H; h += nthreads) {      // the sink is a key of score 0 without a value
+  for (int i = tid; i < H * a.dim; i += NT) q_s[i] = q[i];
+  for (int i = tid; i < H * H; i += NT) t_s[i] = a.talk[i];
+  for (int h = tid; h < H; h += NT) {      // the sink is a key of score 0 without a value
     m_s[h] = a.sink ? 0.f : -INFINITY;
     l_s[h] = a.sink ? 1.f : 0.f;
   }
   __syncthreads();
   const WinVisible vis = win_visible(a, pos);
   // pass 1: maxima and denominators
-  for (int t0 = 0; t0 < vis.count; t0 += TALK_TILE) {
-    const int cnt = vis.count - t0 < TALK_TILE ? vis.count - t0 : TALK_TILE;
-    talk_tile_scores(a, vis, seq, t0, cnt, q_s, p_s, row_s, tid, nthreads);
+  for (int t0 = 0; t0 < vis.count; t0 += tile) {
+    const int cnt = vis.count - t0 < tile ? vis.count - t0 : tile;
+    talk_tile_scores(a, vis, seq, t0, cnt, tile, q_s, p_s, row_s, tid, NT);
     for (int h = warp; h < H; h += n_warps) {
       float top = -INFINITY;
-      for (int jj = lane; jj < cnt; jj += 32) top = fmaxf(top, p_s[h * TALK_TILE + jj]);
+      for (int jj = lane; jj < cnt; jj += 32) top = fmaxf(top, p_s[h * tile + jj]);
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
       const float mn = fmaxf(m_s[h], top);
       float sum = 0.f;
-      for (int jj = lane; jj < cnt; jj += 32) sum += expf(p_s[h * TALK_TILE + jj] - mn);
+      for (int jj = lane; jj < cnt; jj += 32) sum += expf(p_s[h * tile + jj] - mn);
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
       __syncwarp();
@@ -771,7 +772,7 @@ window_attn_talk_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const
     }
     __syncthreads();
   }
-  for (int h = tid; h < H; h += nthreads) l_s[h] = 1.0f / l_s[h];
+  for (int h = tid; h < H; h += NT) l_s[h] = 1.0f / l_s[h];
   __syncthreads();
   // pass 2: final weights, mixed, times the values
   float acc[NACC];
@@ -779,31 +780,43 @@ window_attn_talk_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const
   for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
   const int n_out = H * a.vdim;
   const int v_base = a.kv_heads * a.dim;
-  for (int t0 = 0; t0 < vis.count; t0 += TALK_TILE) {
-    const int cnt = vis.count - t0 < TALK_TILE ? vis.count - t0 : TALK_TILE;
-    talk_tile_scores(a, vis, seq, t0, cnt, q_s, p_s, row_s, tid, nthreads);
-    for (int it = tid; it < H * cnt; it += nthreads) {
+  for (int t0 = 0; t0 < vis.count; t0 += tile) {
+    const int cnt = vis.count - t0 < tile ? vis.count - t0 : tile;
+    const int cnt4 = (cnt + 3) & ~3;
+    talk_tile_scores(a, vis, seq, t0, cnt, tile, q_s, p_s, row_s, tid, NT);
+    for (int it = tid; it < H * cnt; it += NT) {
       const int h = it / cnt, jj = it % cnt;
-      p_s[h * TALK_TILE + jj] = expf(p_s[h * TALK_TILE + jj] - m_s[h]) * l_s[h];
+      p_s[h * tile + jj] = expf(p_s[h * tile + jj] - m_s[h]) * l_s[h];
     }
     __syncthreads();
-    for (int it = tid; it < H * cnt; it += nthreads) {
-      const int h = it / cnt, jj = it % cnt;
+    for (int it = tid; it < H * cnt4; it += NT) {      // keys past the tile's end get weight zero (their row is the tile's first)
+      const int h = it / cnt4, jj = it % cnt4;
       float v = 0.f;
-      for (int g = 0; g < H; ++g) v = fmaf(t_s[h * H + g], p_s[g * TALK_TILE + jj], v);
-      w_s[h * TALK_TILE + jj] = v;
+      if (jj < cnt)
+        for (int g = 0; g < H; ++g) v = fmaf(t_s[h * H + g], p_s[g * tile + jj], v);
+      w_s[h * tile + jj] = v;
     }
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < NACC; ++i) {
-      const int e = tid + i * nthreads;
+      const int e = tid + i * NT;
       if (e < n_out) {
         const int h = e / a.vdim, c = e % a.vdim;
         const int off = v_base + (h / ratio) * a.vdim + c;
-        const float* wh = w_s + h * TALK_TILE;
-        float v = acc[i];
-        for (int jj = 0; jj < cnt; ++jj) v = fmaf(wh[jj], row_s[jj][off], v);
-        acc[i] = v;
+        const float* wh = w_s + h * tile;
+        float v0 = acc[i], v1 = 0.f;
+        for (int jj = 0; jj < cnt4; jj += 4) {      // four keys per read of the weights
+          const float4 w4 = *reinterpret_cast<const float4*>(wh + jj);
+          const float* r0 = row_s[jj];
+          const float* r1 = row_s[jj + 1];
+          const float* r2 = row_s[jj + 2];
+          const float* r3 = row_s[jj + 3];
+          v0 = fmaf(w4.x, r0[off], v0);
+          v1 = fmaf(w4.y, r1[off], v1);
+          v0 = fmaf(w4.z, r2[off], v0);
+          v1 = fmaf(w4.w, r3[off], v1);
+        }
+        acc[i] = v0 + v1;
       }
     }
     __syncthreads();
@@ -811,7 +824,7 @@ window_attn_talk_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const
   const float* gate = a.g_off >= 0 ? a.qkv + (long long)r * a.ld + a.g_off : nullptr;
 #pragma unroll
   for (int i = 0; i < NACC; ++i) {
-    const int e = tid + i * nthreads;
+    const int e = tid + i * NT;
     if (e < n_out) {
       float v = acc[i];
       if (gate != nullptr) v *= 1.0f / (1.0f + expf(-gate[e]));
@@ -822,17 +835,29 @@ window_attn_talk_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const
   }
 }
 
+static size_t talk_smem_bytes(int heads, int dim, int tile) {
+  return (2 * (size_t)tile + (((size_t)heads * dim + 3) & ~(size_t)3) + 2 * (size_t)heads * tile + 2 * (size_t)heads + (size_t)heads * heads) *
+         sizeof(float);
+}
+
 // the dynamic shared-memory limit is raised once per instantiation, and only when a launch needs it (no runtime call on the steady
 // path, so the steady path can be captured into a CUDA graph)
-template <int NACC>
+template <int NACC, int NT>
 static int launch_window_attn_talk(const WinArgs& a, int R, const int* row_seq, const int* row_pos, void* out, long long ldo, int out_fp32,
-                                   size_t smem, cudaStream_t stream) {
+                                   cudaStream_t stream) {
+  // enough keys a tile that its (key, group of four heads) pairs give every thread one, within shared memory
+  const int units = a.kv_heads * ((a.heads / a.kv_heads + 3) / 4);
+  int tile = 64;
+  while (tile < 256 && units * tile < NT && talk_smem_bytes(a.heads, a.dim, 2 * tile) <= 96 * 1024) tile *= 2;
+  while (tile > 16 && talk_smem_bytes(a.heads, a.dim, tile) > 200 * 1024) tile /= 2;
+  const size_t smem = talk_smem_bytes(a.heads, a.dim, tile);
+  LP_REQUIRE(smem <= 200 * 1024, "lp_window_attn_talk: heads=%d dim=%d do not fit shared memory", a.heads, a.dim);
   static size_t have = 48 * 1024;
   if (smem > have) {
-    LP_CHECK_CUDA(cudaFuncSetAttribute(window_attn_talk_kernel<NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    LP_CHECK_CUDA(cudaFuncSetAttribute(window_attn_talk_kernel<NACC, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     have = 200 * 1024;
   }
-  window_attn_talk_kernel<NACC><<<R, TALK_THREADS, smem, stream>>>(a, R, row_seq, row_pos, out, ldo, out_fp32);
+  window_attn_talk_kernel<NACC, NT><<<R, NT, smem, stream>>>(a, R, row_seq, row_pos, tile, out, ldo, out_fp32);
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
   return 0;
@@ -977,14 +1002,16 @@ extern "C" int lp_window_attn_talk(const lp_window_attn_desc* d, int R, const in
   LP_REQUIRE(d->v_inv_freq == nullptr, "lp_window_attn_talk: rotated values are not mixed here");
   if (R <= 0) return 0;
   const int n_out = d->heads * d->vdim;
-  LP_REQUIRE(n_out <= TALK_THREADS * TALK_MAX_ACC, "lp_window_attn_talk: heads * vdim = %d > %d", n_out, TALK_THREADS * TALK_MAX_ACC);
-  const size_t smem = (2 * (size_t)TALK_TILE + (size_t)d->heads * d->dim + 2 * (size_t)d->heads * TALK_TILE + 2 * (size_t)d->heads +
-                       (size_t)d->heads * d->heads) * sizeof(float);
-  LP_REQUIRE(smem <= 200 * 1024, "lp_window_attn_talk: heads=%d dim=%d do not fit shared memory", d->heads, d->dim);
-  const int nacc = (n_out + TALK_THREADS - 1) / TALK_THREADS;
-  if (nacc <= 2) return launch_window_attn_talk<2>(a, R, row_seq, row_pos, out, ldo, out_fp32, smem, stream);
-  if (nacc <= 8) return launch_window_attn_talk<8>(a, R, row_seq, row_pos, out, ldo, out_fp32, smem, stream);
-  return launch_window_attn_talk<TALK_MAX_ACC>(a, R, row_seq, row_pos, out, ldo, out_fp32, smem, stream);
+  LP_REQUIRE(n_out <= 256 * TALK_MAX_ACC, "lp_window_attn_talk: heads * vdim = %d > %d", n_out, 256 * TALK_MAX_ACC);
+  if (R <= WIN_SPLIT_ROWS) {      // few rows (decoding): one CTA per row still, but of 1024 threads
+    if (n_out <= 1024) return launch_window_attn_talk<1, 1024>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
+    if (n_out <= 2048) return launch_window_attn_talk<2, 1024>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
+    if (n_out <= 4096) return launch_window_attn_talk<4, 1024>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
+    return launch_window_attn_talk<8, 1024>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
+  }
+  if (n_out <= 512) return launch_window_attn_talk<2, 256>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
+  if (n_out <= 2048) return launch_window_attn_talk<8, 256>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
+  return launch_window_attn_talk<TALK_MAX_ACC, 256>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
 }
 
 extern "C" int lp_window_attn_tiles(const lp_window_attn_desc* d, int R, const int* row_seq, const int* row_pos, int n_chunks,
