@@ -741,7 +741,8 @@ size_t lp_mlstm_workspace_bytes(int rows, int heads, int vdim);
 int lp_mlstm(const lp_mlstm_desc* desc, int n_seqs, int R, const int* seq_row0, const int* seq_pos0, const int* seq_slot, void* workspace,
              size_t workspace_bytes, void* stream);
 
-/* x[r, 2i] += sin(row_pos[r] * freq[i]), x[r, 2i + 1] += cos(...): absolute sinusoidal positions; freq fp32 [ceil(D / 2)] */
+/* x[r, 2i] += sin(row_pos[r] * f_i), x[r, 2i + 1] += cos(...): absolute sinusoidal positions; freq fp32 [2][ceil(D / 2)] holds every
+ * frequency as two floats, f_i = freq[0][i] + freq[1][i] (a float64 value split on the host) */
 int lp_add_positions_f32(float* x, long long ldx, int R, int D, const int* row_pos, const float* freq, void* stream);
 /* x[r, :] += v for every row */
 int lp_add_row_f32(float* x, long long ldx, const float* v, int M, int N, void* stream);

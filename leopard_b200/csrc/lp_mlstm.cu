@@ -284,9 +284,11 @@ extern "C" int lp_mlstm(const lp_mlstm_desc* d, int n_seqs, int R, const int* se
   const int ns = d->dim <= rows ? 2 : (d->dim + rows - 1) / rows;      // at least two row groups (rows past dim stay zero)
   const size_t smem = ((size_t)2 * MLSTM_TOK * ns * rows + MLSTM_TOK * MLSTM_COLS + (size_t)MLSTM_TOK * ns * MLSTM_COLS + MLSTM_TOK) *
                       sizeof(float);
-  static size_t have = 48 * 1024;      // raised once, and only for head sizes that need it
+  static size_t have8 = 48 * 1024, have16 = 48 * 1024;      // raised once per instantiation, and only for head sizes that need it
+  size_t& have = rows == 8 ? have8 : have16;
   if (smem > have) {
-    LP_CHECK_CUDA(cudaFuncSetAttribute(mlstm_scan_kernel<MLSTM_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    if (rows == 8) LP_CHECK_CUDA(cudaFuncSetAttribute(mlstm_scan_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    else LP_CHECK_CUDA(cudaFuncSetAttribute(mlstm_scan_kernel<MLSTM_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
     have = 96 * 1024;
   }
   mlstm_gate_kernel<<<n_seqs * d->heads, MLSTM_GATE_WARPS * 32, 0, stream>>>(

@@ -7,7 +7,7 @@
 //   lp_glu_f32          elementwise epilogues for matrix products that ran elsewhere: xIELU, squared relu, silu(gate) * up.
 //   lp_axpy_f32         y <- y + alpha x, the residual update after such a product.
 //   lp_add_positions_f32  x[r, 2i] += sin(p f_i), x[r, 2i + 1] += cos(p f_i) with p the row's position: absolute sinusoidal positions
-//                       added to the stream (angles in fp32 from an fp32 frequency table, accurate sincosf).
+//                       added to the stream (fp32 angles with the product's rounding error carried along, accurate sincosf).
 //   lp_add_row_f32      x[r, :] += v for every row (a learned vector that marks a pass of a looped stack).
 //   lp_token_shift_f32  y_t = h_t + (h_(t-1) - h_t) * mu per channel, with h the rows as they came in; the row before a request's
 //                       first row of this step comes from the request's slot (zeros at position 0), and the slot then takes the
@@ -86,18 +86,23 @@ __global__ void axpy_f32_kernel(float* __restrict__ y, long long ldy, const floa
   y[(long long)m * ldy + n] = fmaf(alpha, x[(long long)m * ldx + n], y[(long long)m * ldy + n]);
 }
 
-// pair i of a row: (sin, cos) of position * freq[i]; an odd width leaves the last sine without its cosine
+// pair i of a row: (sin, cos) of position * frequency i; an odd width leaves the last sine without its cosine.  The frequency comes as
+// two floats hi + lo (a float64 value split once on the host), and the product's rounding error is recovered with one fma, so the
+// angle is a = fl(p hi) plus a small rest e known to about 2^-48 of a: sin(a + e) = sin a + e cos a, cos(a + e) = cos a - e sin a.
 __global__ void add_positions_f32_kernel(float* __restrict__ x, long long ldx, int R, int D, const int* __restrict__ row_pos,
-                                         const float* __restrict__ freq) {
+                                         const float* __restrict__ freq, int n_freq) {
   const int r = blockIdx.x;
   if (r >= R) return;
   const float p = (float)row_pos[r];
   float* xr = x + (long long)r * ldx;
   for (int i = threadIdx.x; 2 * i < D; i += blockDim.x) {
+    const float hi = freq[i], lo = freq[n_freq + i];
+    const float a = p * hi;
+    const float e = fmaf(p, hi, -a) + p * lo;
     float s, c;
-    sincosf(p * freq[i], &s, &c);
-    xr[2 * i] += s;
-    if (2 * i + 1 < D) xr[2 * i + 1] += c;
+    sincosf(a, &s, &c);
+    xr[2 * i] += fmaf(e, c, s);
+    if (2 * i + 1 < D) xr[2 * i + 1] += fmaf(-e, s, c);
   }
 }
 
@@ -139,7 +144,7 @@ extern "C" int lp_add_positions_f32(float* x, long long ldx, int R, int D, const
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LP_REQUIRE(x != nullptr && row_pos != nullptr && freq != nullptr && R >= 0 && D > 0, "lp_add_positions_f32: bad arguments");
   if (R == 0) return 0;
-  add_positions_f32_kernel<<<R, 128, 0, stream>>>(x, ldx, R, D, row_pos, freq);
+  add_positions_f32_kernel<<<R, 128, 0, stream>>>(x, ldx, R, D, row_pos, freq, (D + 1) / 2);
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
   return 0;

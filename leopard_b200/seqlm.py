@@ -235,9 +235,11 @@ class SeqLMWeights:
         self.embed = mat(w(None, "embed", (cfg.vocab, D)))
         self.head = mat(w(None, "head", (cfg.vocab, D)))
         self.final_gain = one_plus(None, "final.norm") if vector else num(None, "final.norm")
-        if cfg.position_base > 0:      # frequencies in float64, rounded once
-            i2 = np.arange((D + 1) // 2, dtype=np.float64)
-            self.position_freq = torch.from_numpy((cfg.position_base ** (-2.0 * i2 / D)).astype(np.float32)).to(dev)
+        if cfg.position_base > 0:      # frequencies in float64, split into two floats hi + lo
+            f64 = cfg.position_base ** (-2.0 * np.arange((D + 1) // 2, dtype=np.float64) / D)
+            hi = f64.astype(np.float32)
+            lo = (f64 - hi.astype(np.float64)).astype(np.float32)
+            self.position_freq = torch.from_numpy(np.concatenate([hi, lo])).to(dev)
         # vectors added to the stream before a layer: per layer of the list, also for one that runs on another layer's tensors
         self.add_before: List[Optional[torch.Tensor]] = []
         for lc in cfg.layers:
