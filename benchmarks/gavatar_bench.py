@@ -120,6 +120,8 @@ def bench_gavatar(name, s, dev, steps, warmup, peaks, prompt):
 
     def per_s(key, amount, unit):
         return round(amount / (kp[key]["ms"] * 1e-3) / unit, 2) if key in kp and kp[key]["ms"] > 0 else None
+    if "lp_window_attn_talk_tiles" in kp:      # prompts take the row-tile entry of the same kernel
+        kp["lp_window_attn_talk"] = kp["lp_window_attn_talk_tiles"]
     r = {"lp_gemm_bf16_tflops": per_s("lp_gemm_bf16", flops_gemm, 1e12), "lp_latent_attend_tflops": per_s("lp_latent_attend", lat_flops, 1e12),
          "lp_window_attn_talk_tflops": per_s("lp_window_attn_talk", talk_flops, 1e12), "lp_mlstm_tflops": per_s("lp_mlstm", mem_flops, 1e12),
          "lp_token_shift_gbs": per_s("lp_token_shift_f32", RUNS * R * D * (4.0 + 2.0), 1e9)}

@@ -699,6 +699,11 @@ int lp_window_attn(const lp_window_attn_desc* desc, int R, const int* row_seq, c
  * the values of its own key / value head; every visibility rule, the cap and the sink as above; the gate of g_off when it is given */
 int lp_window_attn_talk(const lp_window_attn_desc* desc, int R, const int* row_seq, const int* row_pos, void* out, long long ldo,
                         int out_fp32, void* stream);
+/* the same result for the rows of prompts and portions, per tile of consecutive rows of one request (chunk tables as for
+ * lp_window_attn_tiles): the rows of a tile share the keys and values they read */
+int lp_window_attn_talk_tiles(const lp_window_attn_desc* desc, int R, const int* row_seq, const int* row_pos, int n_chunks,
+                              const int* chunk_seq, const int* chunk_row0, const int* chunk_len, void* out, long long ldo, int out_fp32,
+                              void* stream);
 /* the same result for the rows of prompts, computed per tile of consecutive rows of one request: the chunk tables of
  * lp_retention_prefill (at most LP_RETENTION_CHUNK rows a chunk, never across requests) say which rows belong together */
 int lp_window_attn_tiles(const lp_window_attn_desc* desc, int R, const int* row_seq, const int* row_pos, int n_chunks, const int* chunk_seq,

@@ -224,6 +224,7 @@ _SIGS = {
     "lp_window_attn": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _vp, _ll, _i, _vp]),
     "lp_window_attn_tiles": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _i, _vp]),
     "lp_window_attn_talk": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _vp, _ll, _i, _vp]),
+    "lp_window_attn_talk_tiles": (_i, [C.POINTER(WindowAttnDesc), _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _i, _vp]),
     "lp_mlstm_workspace_bytes": (_sz, [_i, _i, _i]),
     "lp_mlstm": (_i, [C.POINTER(MLSTMDesc), _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
     "lp_add_positions_f32": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp]),
@@ -290,7 +291,7 @@ STREAM32_SYMBOLS = ("lp_last_error", "lp_abi_version", "lp_launch_count", "lp_li
                     "lp_retention_decode", "lp_latent_prep", "lp_latent_attend", "lp_moe_route", "lp_moe_max_tiles", "lp_moe_align",
                     "lp_moe_combine", "lp_axpy_f32", "lp_window_attn_prep", "lp_window_attn_pool", "lp_window_attn", "lp_window_attn_tiles",
                     "lp_mingru_workspace_bytes",
-                    "lp_mingru_prefill", "lp_mingru_decode", "lp_window_attn_talk", "lp_mlstm_workspace_bytes", "lp_mlstm",
+                    "lp_mingru_prefill", "lp_mingru_decode", "lp_window_attn_talk", "lp_window_attn_talk_tiles", "lp_mlstm_workspace_bytes", "lp_mlstm",
                     "lp_add_positions_f32", "lp_add_row_f32", "lp_token_shift_f32", "lp_moe_route_softmax")
 STREAM32_OPTIONAL = ("lp_gemm_bf16",)      # present in the native libraries, absent from the CPU-emulated build
 _stream32 = None

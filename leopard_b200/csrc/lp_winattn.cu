@@ -24,6 +24,7 @@
 //   lp_window_attn_talk   one CTA per row and ALL heads, two passes over the visible keys in tiles: the first finds every head's
 //                         softmax maximum and denominator, the second computes the scores again, normalises them, mixes them over
 //                         the heads in shared memory and adds the values with the mixed weights.
+//   lp_window_attn_talk_tiles  the same for prompts, a CTA per tile of 4 consecutive rows of a request and all heads.
 //   lp_window_attn_tiles  the same for prompts, a CTA per tile of 2 or 4 consecutive rows of a request: the rows share every key and
 //                         value row the tile reads, each (row, key) pair masked by the row's own rule.
 #include "lp_host.h"
@@ -666,20 +667,34 @@ window_attn_tile_kernel(WinArgs a, int n_chunks, const int* __restrict__ chunk_s
 
 // Talking heads: the softmax weights of all heads are mixed, weight_h(i, j) <- sum_g talk[h, g] weight_g(i, j), before head h applies
 // them to the values of its own key / value head — so a row needs the NORMALISED weights of every head at every key.  One CTA per
-// row and all heads; the visible keys (the same index space as above: kept tokens, pooled blocks, window) are walked twice in tiles
+// row (or tile of rows) and all heads; the visible keys (the same index space as above: kept tokens, pooled blocks, window) are walked twice in tiles
 // of 64 to 256 keys.  Pass 1: scores of the tile for every head -> running maximum and denominator per head.  Pass 2: the same
 // scores again (the same arithmetic, so the same numbers), weights = exp(score - max) / denominator, mixed over the heads in shared
 // memory, then every thread adds the tile's values to the (head, value channel) sums it owns.  Nothing is rescaled in pass 2: the
 // weights are final.  An output gate, when the description names one, multiplies the sums by sigmoid(g) on the way out.
 constexpr int TALK_MAX_ACC = 32;      // heads * vdim <= 256 * TALK_MAX_ACC
 
-// scores of one tile -> p_s[h][jj] (scaled and capped); a thread takes one key and up to four query heads of one key / value head
-__device__ __forceinline__ void talk_tile_scores(const WinArgs& a, const WinVisible& vis, int seq, int t0, int cnt, int tile, const float* q_s,
-                                                 float* p_s, const float** row_s, int tid, int nthreads) {
-  const int ratio = a.heads / a.kv_heads;
+// what the rows of a tile see: every row's own rule, and the union that the tile walks (the index space of win_visible_row)
+template <int RQ>
+struct TalkRows {
+  int keep[RQ], blocks[RQ], lo[RQ];
+  int pos0, nrows;
+  WinVisible uni;
+};
+
+// scores of one tile of keys -> p_s[row][h][jj] (scaled and capped; -inf where the row does not see the key); a thread takes one key
+// and up to four query heads of one key / value head, for all RQ rows, so a key is read once for the whole tile of rows.  With
+// `final_w` the maxima and inverse denominators are known and the thread writes the weight exp(score - max) / denominator (0 where
+// the row does not see the key).
+template <int RQ>
+__device__ __forceinline__ void talk_tile_scores(const WinArgs& a, const TalkRows<RQ>& tr, int seq, int t0, int cnt, int tile, int hd4,
+                                                 const float* q_s, float* p_s, const float** row_s, const float* m_s, const float* linv_s,
+                                                 bool final_w, int tid, int nthreads) {
+  const int H = a.heads, ratio = a.heads / a.kv_heads;
   const int hgroups = (ratio + 3) / 4;      // groups of at most four query heads per key / value head
   const int cnt4 = (cnt + 3) & ~3;
-  for (int jj = tid; jj < cnt4; jj += nthreads) row_s[jj] = win_visible_row(a, vis, seq, t0 + (jj < cnt ? jj : 0));
+  const WinVisible& uni = tr.uni;
+  for (int jj = tid; jj < cnt4; jj += nthreads) row_s[jj] = win_visible_row(a, uni, seq, t0 + (jj < cnt ? jj : 0));
   __syncthreads();
   const bool vec = (a.dim % 4 == 0) && (a.vdim % 4 == 0);
   for (int it = tid; it < a.kv_heads * hgroups * cnt; it += nthreads) {
@@ -687,18 +702,25 @@ __device__ __forceinline__ void talk_tile_scores(const WinArgs& a, const WinVisi
     const int g = u / hgroups, h0 = g * ratio + (u % hgroups) * 4;
     const int nh = (g + 1) * ratio - h0 < 4 ? (g + 1) * ratio - h0 : 4;
     const float* kp = row_s[jj] + g * a.dim;
-    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    float sc[RQ][4];
+#pragma unroll
+    for (int rq = 0; rq < RQ; ++rq)
+#pragma unroll
+      for (int h = 0; h < 4; ++h) sc[rq][h] = 0.f;
     if (vec) {
       for (int d = 0; d < a.dim; d += 4) {
         const float4 k4 = *reinterpret_cast<const float4*>(kp + d);
 #pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          if (h < nh) {
-            const float4 q4 = *reinterpret_cast<const float4*>(q_s + (h0 + h) * a.dim + d);
-            sc[h] = fmaf(q4.x, k4.x, sc[h]);
-            sc[h] = fmaf(q4.y, k4.y, sc[h]);
-            sc[h] = fmaf(q4.z, k4.z, sc[h]);
-            sc[h] = fmaf(q4.w, k4.w, sc[h]);
+        for (int rq = 0; rq < RQ; ++rq) {
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            if (h < nh) {
+              const float4 q4 = *reinterpret_cast<const float4*>(q_s + rq * hd4 + (h0 + h) * a.dim + d);
+              sc[rq][h] = fmaf(q4.x, k4.x, sc[rq][h]);
+              sc[rq][h] = fmaf(q4.y, k4.y, sc[rq][h]);
+              sc[rq][h] = fmaf(q4.z, k4.z, sc[rq][h]);
+              sc[rq][h] = fmaf(q4.w, k4.w, sc[rq][h]);
+            }
           }
         }
       }
@@ -706,161 +728,305 @@ __device__ __forceinline__ void talk_tile_scores(const WinArgs& a, const WinVisi
       for (int d = 0; d < a.dim; ++d) {
         const float kv = kp[d];
 #pragma unroll
-        for (int h = 0; h < 4; ++h)
-          if (h < nh) sc[h] = fmaf(q_s[(h0 + h) * a.dim + d], kv, sc[h]);
+        for (int rq = 0; rq < RQ; ++rq)
+#pragma unroll
+          for (int h = 0; h < 4; ++h)
+            if (h < nh) sc[rq][h] = fmaf(q_s[rq * hd4 + (h0 + h) * a.dim + d], kv, sc[rq][h]);
       }
     }
+    // which of the tile's rows see this key
+    const int t = t0 + jj;
+    const int seg = t < uni.n_keep ? 0 : (t < uni.n_keep + uni.n_blocks ? 1 : 2);
+    const int idx = seg == 0 ? t : (seg == 1 ? t - uni.n_keep : uni.lo + (t - uni.n_keep - uni.n_blocks));
 #pragma unroll
-    for (int h = 0; h < 4; ++h) {
-      if (h < nh) {
-        float v = sc[h] * a.scale;
-        if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
-        p_s[(h0 + h) * tile + jj] = v;
+    for (int rq = 0; rq < RQ; ++rq) {
+      bool seen = rq < tr.nrows;
+      if (seg == 0) seen = seen && idx < tr.keep[rq];
+      else if (seg == 1) seen = seen && idx < tr.blocks[rq];
+      else seen = seen && idx >= tr.lo[rq] && idx <= tr.pos0 + rq;
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        if (h < nh) {
+          float v = sc[rq][h] * a.scale;
+          if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+          if (final_w) v = seen ? expf(v - m_s[rq * H + h0 + h]) * linv_s[rq * H + h0 + h] : 0.f;
+          else if (!seen) v = -INFINITY;
+          p_s[(rq * H + h0 + h) * tile + jj] = v;
+        }
       }
     }
   }
   __syncthreads();
 }
 
-// `tile` keys at a time (a multiple of 4, chosen by the host so that a tile's (key, head group) pairs occupy the CTA's threads)
-template <int NACC, int NT>
+// One CTA per tile of RQ consecutive rows of one request (RQ = 1: per row) and ALL heads; `tile` keys at a time (a multiple of 4,
+// chosen by the host so that a tile's (key, head group) pairs occupy the CTA's threads).  The tile of rows walks the UNION of what
+// its rows see and every (row, key) pair is masked by the row's own rule, as in the row-tile kernel above.
+// Pass 2 per tile of keys: weights p_s[row][h][key] -> mixed weights w_s[key][row][h] (a thread per key, row and four output heads;
+// the mixing matrix lies transposed and padded, so one 16-byte read brings four heads' factors) -> sums: a thread owns a value
+// channel of one key / value head and QH query heads of it (QH = 4, 2 or 1, whichever divides the heads per key head) for every row,
+// so one value read and RQ weight reads of 16, 8 or 4 bytes feed RQ * QH sums.  When the (head group, channel) units are fewer than
+// the threads, `slices` threads share a unit, each taking every slices-th key, and their sums meet in shared memory at the end.
+template <int QH, int NACC, int NT, int RQ>
 __global__ void __launch_bounds__(NT)
-window_attn_talk_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const int* __restrict__ row_pos, int tile, void* __restrict__ out,
-                        long long ldo, int out_fp32) {
+window_attn_talk_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const int* __restrict__ row_pos, int n_chunks,
+                        const int* __restrict__ chunk_seq, const int* __restrict__ chunk_row0, const int* __restrict__ chunk_len,
+                        int tiles_per_chunk, int tile, int slices, void* __restrict__ out, long long ldo, int out_fp32) {
   extern __shared__ float dyn_smem[];
-  const int r = blockIdx.x;
-  if (r >= R) return;
+  int r0, seq;
+  TalkRows<RQ> tr;
+  if (RQ == 1) {
+    r0 = blockIdx.x;
+    if (r0 >= R) return;
+    tr.nrows = 1;
+    seq = row_seq[r0];
+  } else {
+    const int c = blockIdx.x / tiles_per_chunk, sub = blockIdx.x % tiles_per_chunk;
+    if (c >= n_chunks) return;
+    const int len = chunk_len[c];
+    if (sub * RQ >= len) return;
+    r0 = chunk_row0[c] + sub * RQ;
+    tr.nrows = len - sub * RQ < RQ ? len - sub * RQ : RQ;
+    seq = chunk_seq[c];
+  }
+  tr.pos0 = row_pos[r0];
+  const int nrows = tr.nrows;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr int n_warps = NT / 32;
-  const int H = a.heads, ratio = a.heads / a.kv_heads;
+  const int H = a.heads, ratio = a.heads / a.kv_heads, Hp = (H + 3) & ~3, hg4 = Hp >> 2, hd4 = (H * a.dim + 3) & ~3;
   const float** row_s = reinterpret_cast<const float**>(dyn_smem);      // [tile] cache row of each key of the tile
-  float* q_s = dyn_smem + 2 * tile;             // [H][dim]
-  float* p_s = q_s + ((H * a.dim + 3) & ~3);    // [H][tile] scores, then weights
-  float* w_s = p_s + H * tile;                  // [H][tile] mixed weights
-  float* m_s = w_s + H * tile;                  // [H] maxima
-  float* l_s = m_s + H;                         // [H] denominators, then their inverses
-  float* t_s = l_s + H;                         // [H][H] the mixing matrix
-  const int seq = row_seq[r], pos = row_pos[r];
-  const float* q = a.qkv + (long long)r * a.ld + a.q_off;
-  for (int i = tid; i < H * a.dim; i += NT) q_s[i] = q[i];
-  for (int i = tid; i < H * H; i += NT) t_s[i] = a.talk[i];
-  for (int h = tid; h < H; h += NT) {      // the sink is a key of score 0 without a value
-    m_s[h] = a.sink ? 0.f : -INFINITY;
-    l_s[h] = a.sink ? 1.f : 0.f;
+  float* q_s = dyn_smem + 2 * tile;             // [RQ][H][dim]
+  float* p_s = q_s + RQ * hd4;                  // [RQ][H][tile] scores (pass 1), weights (pass 2)
+  float* w_s = p_s + RQ * H * tile;             // [tile][RQ][Hp] mixed weights
+  float* t_s = w_s + RQ * Hp * tile;            // [H][Hp] the mixing matrix, transposed: t_s[g][h] = talk[h][g]
+  float* m_s = t_s + H * Hp;                    // [RQ][H] maxima
+  float* l_s = m_s + RQ * H;                    // [RQ][H] denominators, then their inverses
+  float* red_s = l_s + RQ * H;                  // [slices][units][RQ][QH] partial sums, when slices > 1
+  for (int i = tid; i < RQ * H * a.dim; i += NT) {
+    const int rq = i / (H * a.dim), e = i % (H * a.dim);
+    q_s[rq * hd4 + e] = rq < nrows ? a.qkv[(long long)(r0 + rq) * a.ld + a.q_off + e] : 0.f;
   }
+  for (int i = tid; i < H * Hp; i += NT) {
+    const int g = i / Hp, h = i % Hp;
+    t_s[i] = h < H ? a.talk[h * H + g] : 0.f;
+  }
+  for (int i = tid; i < RQ * H; i += NT) {      // the sink is a key of score 0 without a value
+    m_s[i] = a.sink ? 0.f : -INFINITY;
+    l_s[i] = a.sink ? 1.f : 0.f;
+  }
+#pragma unroll
+  for (int rq = 0; rq < RQ; ++rq) {
+    const WinVisible v = win_visible(a, tr.pos0 + (rq < nrows ? rq : nrows - 1));
+    tr.keep[rq] = v.n_keep;
+    tr.blocks[rq] = v.n_blocks;
+    tr.lo[rq] = v.lo;
+  }
+  {
+    const WinVisible last = win_visible(a, tr.pos0 + nrows - 1);
+    tr.uni.n_keep = last.n_keep;
+    tr.uni.n_blocks = last.n_blocks;
+    tr.uni.lo = tr.lo[0];
+    tr.uni.count = last.n_keep + last.n_blocks + (tr.pos0 + nrows - 1 - tr.lo[0] + 1);
+  }
+  const int count = tr.uni.count;
   __syncthreads();
-  const WinVisible vis = win_visible(a, pos);
   // pass 1: maxima and denominators
-  for (int t0 = 0; t0 < vis.count; t0 += tile) {
-    const int cnt = vis.count - t0 < tile ? vis.count - t0 : tile;
-    talk_tile_scores(a, vis, seq, t0, cnt, tile, q_s, p_s, row_s, tid, NT);
-    for (int h = warp; h < H; h += n_warps) {
+  for (int t0 = 0; t0 < count; t0 += tile) {
+    const int cnt = count - t0 < tile ? count - t0 : tile;
+    talk_tile_scores<RQ>(a, tr, seq, t0, cnt, tile, hd4, q_s, p_s, row_s, nullptr, nullptr, false, tid, NT);
+    for (int x = warp; x < nrows * H; x += n_warps) {      // x = row * H + head
       float top = -INFINITY;
-      for (int jj = lane; jj < cnt; jj += 32) top = fmaxf(top, p_s[h * tile + jj]);
+      for (int jj = lane; jj < cnt; jj += 32) top = fmaxf(top, p_s[x * tile + jj]);
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
-      const float mn = fmaxf(m_s[h], top);
+      const float mn = fmaxf(m_s[x], top);
+      const float ref = mn == -INFINITY ? 0.f : mn;      // a row that has seen nothing yet, and sees nothing in this tile
       float sum = 0.f;
-      for (int jj = lane; jj < cnt; jj += 32) sum += expf(p_s[h * tile + jj] - mn);
+      for (int jj = lane; jj < cnt; jj += 32) sum += expf(p_s[x * tile + jj] - ref);
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
       __syncwarp();
       if (lane == 0) {
-        l_s[h] = fmaf(l_s[h], expf(m_s[h] - mn), sum);      // exp(-inf) = 0 on the first tile
-        m_s[h] = mn;
+        l_s[x] = fmaf(l_s[x], expf(m_s[x] - ref), sum);      // exp(-inf) = 0 on the first tile
+        m_s[x] = mn;
       }
     }
     __syncthreads();
   }
-  for (int h = tid; h < H; h += NT) l_s[h] = 1.0f / l_s[h];
+  for (int i = tid; i < nrows * H; i += NT) l_s[i] = 1.0f / l_s[i];
   __syncthreads();
   // pass 2: final weights, mixed, times the values
-  float acc[NACC];
+  float acc[NACC][RQ][QH];
 #pragma unroll
-  for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
-  const int n_out = H * a.vdim;
+  for (int i = 0; i < NACC; ++i)
+#pragma unroll
+    for (int rq = 0; rq < RQ; ++rq)
+#pragma unroll
+      for (int x = 0; x < QH; ++x) acc[i][rq][x] = 0.f;
+  const int nqg = ratio / QH;                       // query-head groups per key / value head
+  const int units = a.kv_heads * nqg * a.vdim;      // (key / value head, query group, channel)
   const int v_base = a.kv_heads * a.dim;
-  for (int t0 = 0; t0 < vis.count; t0 += tile) {
-    const int cnt = vis.count - t0 < tile ? vis.count - t0 : tile;
-    const int cnt4 = (cnt + 3) & ~3;
-    talk_tile_scores(a, vis, seq, t0, cnt, tile, q_s, p_s, row_s, tid, NT);
-    for (int it = tid; it < H * cnt; it += NT) {
-      const int h = it / cnt, jj = it % cnt;
-      p_s[h * tile + jj] = expf(p_s[h * tile + jj] - m_s[h]) * l_s[h];
-    }
-    __syncthreads();
-    for (int it = tid; it < H * cnt4; it += NT) {      // keys past the tile's end get weight zero (their row is the tile's first)
-      const int h = it / cnt4, jj = it % cnt4;
-      float v = 0.f;
-      if (jj < cnt)
-        for (int g = 0; g < H; ++g) v = fmaf(t_s[h * H + g], p_s[g * tile + jj], v);
-      w_s[h * tile + jj] = v;
+  for (int t0 = 0; t0 < count; t0 += tile) {
+    const int cnt = count - t0 < tile ? count - t0 : tile;
+    talk_tile_scores<RQ>(a, tr, seq, t0, cnt, tile, hd4, q_s, p_s, row_s, m_s, l_s, true, tid, NT);
+    for (int it = tid; it < hg4 * RQ * cnt; it += NT) {
+      const int hq = it % hg4, rq = (it / hg4) % RQ, jj = it / (hg4 * RQ);
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float* pp = p_s + rq * H * tile + jj;
+      for (int g = 0; g < H; ++g) {
+        const float p = pp[g * tile];
+        const float4 t4 = *reinterpret_cast<const float4*>(t_s + g * Hp + 4 * hq);
+        v.x = fmaf(t4.x, p, v.x);
+        v.y = fmaf(t4.y, p, v.y);
+        v.z = fmaf(t4.z, p, v.z);
+        v.w = fmaf(t4.w, p, v.w);
+      }
+      *reinterpret_cast<float4*>(w_s + (jj * RQ + rq) * Hp + 4 * hq) = v;
     }
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < NACC; ++i) {
       const int e = tid + i * NT;
-      if (e < n_out) {
-        const int h = e / a.vdim, c = e % a.vdim;
-        const int off = v_base + (h / ratio) * a.vdim + c;
-        const float* wh = w_s + h * tile;
-        float v0 = acc[i], v1 = 0.f;
-        for (int jj = 0; jj < cnt4; jj += 4) {      // four keys per read of the weights
-          const float4 w4 = *reinterpret_cast<const float4*>(wh + jj);
-          const float* r0 = row_s[jj];
-          const float* r1 = row_s[jj + 1];
-          const float* r2 = row_s[jj + 2];
-          const float* r3 = row_s[jj + 3];
-          v0 = fmaf(w4.x, r0[off], v0);
-          v1 = fmaf(w4.y, r1[off], v1);
-          v0 = fmaf(w4.z, r2[off], v0);
-          v1 = fmaf(w4.w, r3[off], v1);
+      if (e < units * slices) {
+        const int sl = e / units, u = e % units;
+        const int c = u % a.vdim, gq = u / a.vdim;      // gq = g * nqg + query group, so its first head is gq * QH
+        const int off = v_base + (gq / nqg) * a.vdim + c;
+        const float* wh = w_s + gq * QH;
+#pragma unroll 2
+        for (int jj = sl; jj < cnt; jj += slices) {
+          const float v = row_s[jj][off];
+#pragma unroll
+          for (int rq = 0; rq < RQ; ++rq) {
+            const float* wp = wh + (jj * RQ + rq) * Hp;
+            if (QH == 4) {
+              const float4 w4 = *reinterpret_cast<const float4*>(wp);
+              acc[i][rq][0] = fmaf(w4.x, v, acc[i][rq][0]);
+              acc[i][rq][1 % QH] = fmaf(w4.y, v, acc[i][rq][1 % QH]);
+              acc[i][rq][2 % QH] = fmaf(w4.z, v, acc[i][rq][2 % QH]);
+              acc[i][rq][3 % QH] = fmaf(w4.w, v, acc[i][rq][3 % QH]);
+            } else if (QH == 2) {
+              const float2 w2 = *reinterpret_cast<const float2*>(wp);
+              acc[i][rq][0] = fmaf(w2.x, v, acc[i][rq][0]);
+              acc[i][rq][1 % QH] = fmaf(w2.y, v, acc[i][rq][1 % QH]);
+            } else {
+              acc[i][rq][0] = fmaf(wp[0], v, acc[i][rq][0]);
+            }
+          }
         }
-        acc[i] = v0 + v1;
       }
     }
     __syncthreads();
   }
-  const float* gate = a.g_off >= 0 ? a.qkv + (long long)r * a.ld + a.g_off : nullptr;
+  if (slices > 1) {      // NACC is 1 here: every thread holds one unit's sums over its keys
+    if (tid < units * slices) {
+#pragma unroll
+      for (int rq = 0; rq < RQ; ++rq)
+#pragma unroll
+        for (int x = 0; x < QH; ++x) red_s[(tid * RQ + rq) * QH + x] = acc[0][rq][x];
+    }
+    __syncthreads();
+    if (tid < units) {
+#pragma unroll
+      for (int rq = 0; rq < RQ; ++rq)
+#pragma unroll
+        for (int x = 0; x < QH; ++x) {
+          float v = 0.f;
+          for (int sl = 0; sl < slices; ++sl) v += red_s[((sl * units + tid) * RQ + rq) * QH + x];
+          acc[0][rq][x] = v;
+        }
+    }
+  }
 #pragma unroll
   for (int i = 0; i < NACC; ++i) {
-    const int e = tid + i * NT;
-    if (e < n_out) {
-      float v = acc[i];
-      if (gate != nullptr) v *= 1.0f / (1.0f + expf(-gate[e]));
-      const long long at = (long long)r * ldo + e;
-      if (out_fp32) reinterpret_cast<float*>(out)[at] = v;
-      else reinterpret_cast<bf16*>(out)[at] = __float2bfloat16(v);
+    const int u = tid + i * NT;
+    if (u < units) {
+      const int c = u % a.vdim, gq = u / a.vdim;
+#pragma unroll
+      for (int rq = 0; rq < RQ; ++rq) {
+        if (rq < nrows) {
+          const float* gate = a.g_off >= 0 ? a.qkv + (long long)(r0 + rq) * a.ld + a.g_off : nullptr;
+#pragma unroll
+          for (int x = 0; x < QH; ++x) {
+            const int e = (gq * QH + x) * a.vdim + c;
+            float v = acc[i][rq][x];
+            if (gate != nullptr) v *= 1.0f / (1.0f + expf(-gate[e]));
+            const long long at = (long long)(r0 + rq) * ldo + e;
+            if (out_fp32) reinterpret_cast<float*>(out)[at] = v;
+            else reinterpret_cast<bf16*>(out)[at] = __float2bfloat16(v);
+          }
+        }
+      }
     }
   }
 }
 
-static size_t talk_smem_bytes(int heads, int dim, int tile) {
-  return (2 * (size_t)tile + (((size_t)heads * dim + 3) & ~(size_t)3) + 2 * (size_t)heads * tile + 2 * (size_t)heads + (size_t)heads * heads) *
-         sizeof(float);
+static size_t talk_smem_bytes(int heads, int dim, int tile, int rq, int red_floats) {
+  const size_t hp = ((size_t)heads + 3) & ~(size_t)3;
+  return (2 * (size_t)tile + rq * (((size_t)heads * dim + 3) & ~(size_t)3) + rq * (size_t)heads * tile + rq * hp * tile + (size_t)heads * hp +
+          2 * rq * (size_t)heads + (size_t)red_floats) * sizeof(float);
 }
 
+struct TalkChunks {
+  int n_chunks;
+  const int *seq, *row0, *len;
+};
+
 // the dynamic shared-memory limit is raised once per instantiation, and only when a launch needs it (no runtime call on the steady
-// path, so the steady path can be captured into a CUDA graph)
-template <int NACC, int NT>
-static int launch_window_attn_talk(const WinArgs& a, int R, const int* row_seq, const int* row_pos, void* out, long long ldo, int out_fp32,
-                                   cudaStream_t stream) {
+// path, so the steady path can be captured into a CUDA graph).  0: launched; 1: a tile of RQ > 1 rows does not fit shared memory.
+template <int QH, int NACC, int NT, int RQ>
+static int launch_window_attn_talk(const WinArgs& a, int R, const int* row_seq, const int* row_pos, const TalkChunks& ch, void* out,
+                                   long long ldo, int out_fp32, cudaStream_t stream) {
+  const int n_units = a.heads / QH * a.vdim;
+  const int slices = n_units < NT ? NT / n_units : 1;
+  const int red = slices > 1 ? NT * RQ * QH : 0;
   // enough keys a tile that its (key, group of four heads) pairs give every thread one, within shared memory
   const int units = a.kv_heads * ((a.heads / a.kv_heads + 3) / 4);
   int tile = 64;
-  while (tile < 256 && units * tile < NT && talk_smem_bytes(a.heads, a.dim, 2 * tile) <= 96 * 1024) tile *= 2;
-  while (tile > 16 && talk_smem_bytes(a.heads, a.dim, tile) > 200 * 1024) tile /= 2;
-  const size_t smem = talk_smem_bytes(a.heads, a.dim, tile);
+  while (tile < 256 && units * tile < NT && talk_smem_bytes(a.heads, a.dim, 2 * tile, RQ, red) <= 96 * 1024) tile *= 2;
+  while (tile > 16 && talk_smem_bytes(a.heads, a.dim, tile, RQ, red) > 200 * 1024) tile /= 2;
+  const size_t smem = talk_smem_bytes(a.heads, a.dim, tile, RQ, red);
+  if (RQ > 1 && smem > 100 * 1024) return 1;
   LP_REQUIRE(smem <= 200 * 1024, "lp_window_attn_talk: heads=%d dim=%d do not fit shared memory", a.heads, a.dim);
   static size_t have = 48 * 1024;
   if (smem > have) {
-    LP_CHECK_CUDA(cudaFuncSetAttribute(window_attn_talk_kernel<NACC, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    LP_CHECK_CUDA(cudaFuncSetAttribute(window_attn_talk_kernel<QH, NACC, NT, RQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     have = 200 * 1024;
   }
-  window_attn_talk_kernel<NACC, NT><<<R, NT, smem, stream>>>(a, R, row_seq, row_pos, tile, out, ldo, out_fp32);
+  int grid = R, tiles = 0;
+  if (RQ > 1) {
+    const int longest = R < LP_RETENTION_CHUNK ? R : LP_RETENTION_CHUNK;      // no chunk has more rows than the step or the chunk size
+    tiles = (longest + RQ - 1) / RQ;
+    grid = ch.n_chunks * tiles;
+  }
+  window_attn_talk_kernel<QH, NACC, NT, RQ><<<grid, NT, smem, stream>>>(a, R, row_seq, row_pos, ch.n_chunks, ch.seq, ch.row0, ch.len, tiles,
+                                                                        tile, slices, out, ldo, out_fp32);
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
   return 0;
+}
+
+// the instantiation whose threads hold the fewest sums that still cover all (head group, channel) units; with chunk tables
+// (prompts and portions) tiles of TALK_RQ rows where a thread's sums stay few, else (and for one-token steps) a CTA per row
+constexpr int TALK_RQ = 4;
+template <int QH, int NT>
+static int pick_window_attn_talk(const WinArgs& a, int R, const int* row_seq, const int* row_pos, const TalkChunks& ch, void* out, long long ldo,
+                                 int out_fp32, cudaStream_t stream) {
+  const int per_thread = (a.heads / QH * a.vdim + NT - 1) / NT;
+  if constexpr (NT == 256) {
+   if (ch.n_chunks > 0 && per_thread * QH <= 8) {
+    int rc;
+    if (per_thread <= 1) rc = launch_window_attn_talk<QH, 1, NT, TALK_RQ>(a, R, row_seq, row_pos, ch, out, ldo, out_fp32, stream);
+    else if (per_thread <= 2) rc = launch_window_attn_talk<QH, 2, NT, TALK_RQ>(a, R, row_seq, row_pos, ch, out, ldo, out_fp32, stream);
+    else rc = launch_window_attn_talk<QH, 8 / QH, NT, TALK_RQ>(a, R, row_seq, row_pos, ch, out, ldo, out_fp32, stream);
+    if (rc != 1) return rc;
+   }
+  }
+  if (per_thread <= 1) return launch_window_attn_talk<QH, 1, NT, 1>(a, R, row_seq, row_pos, ch, out, ldo, out_fp32, stream);
+  if (per_thread <= 2) return launch_window_attn_talk<QH, 2, NT, 1>(a, R, row_seq, row_pos, ch, out, ldo, out_fp32, stream);
+  if (per_thread <= 8) return launch_window_attn_talk<QH, 8, NT, 1>(a, R, row_seq, row_pos, ch, out, ldo, out_fp32, stream);
+  if (per_thread <= 32 / QH) return launch_window_attn_talk<QH, 32 / QH, NT, 1>(a, R, row_seq, row_pos, ch, out, ldo, out_fp32, stream);
+  LP_REQUIRE(false, "lp_window_attn_talk: heads * vdim = %d is more than %d threads hold", a.heads * a.vdim, NT);
+  return 1;
 }
 
 static int fill_win(WinArgs& a, const lp_window_attn_desc* d, bool need_q) {
@@ -993,9 +1159,8 @@ extern "C" int lp_window_attn(const lp_window_attn_desc* d, int R, const int* ro
   return launch_window_attn<1>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
 }
 
-extern "C" int lp_window_attn_talk(const lp_window_attn_desc* d, int R, const int* row_seq, const int* row_pos, void* out, long long ldo,
-                                   int out_fp32, void* stream_) {
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+static int window_attn_talk(const lp_window_attn_desc* d, int R, const int* row_seq, const int* row_pos, const TalkChunks& ch, void* out,
+                            long long ldo, int out_fp32, cudaStream_t stream) {
   WinArgs a;
   if (int rc = fill_win(a, d, true)) return rc;
   LP_REQUIRE(out != nullptr && row_seq != nullptr && row_pos != nullptr && d->talk != nullptr, "lp_window_attn_talk: null operand");
@@ -1003,15 +1168,32 @@ extern "C" int lp_window_attn_talk(const lp_window_attn_desc* d, int R, const in
   if (R <= 0) return 0;
   const int n_out = d->heads * d->vdim;
   LP_REQUIRE(n_out <= 256 * TALK_MAX_ACC, "lp_window_attn_talk: heads * vdim = %d > %d", n_out, 256 * TALK_MAX_ACC);
-  if (R <= WIN_SPLIT_ROWS) {      // few rows (decoding): one CTA per row still, but of 1024 threads
-    if (n_out <= 1024) return launch_window_attn_talk<1, 1024>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
-    if (n_out <= 2048) return launch_window_attn_talk<2, 1024>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
-    if (n_out <= 4096) return launch_window_attn_talk<4, 1024>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
-    return launch_window_attn_talk<8, 1024>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
+  const int ratio = d->heads / d->kv_heads;
+  const int qh = ratio % 4 == 0 ? 4 : ratio % 2 == 0 ? 2 : 1;
+  if (ch.n_chunks == 0 && R <= WIN_SPLIT_ROWS && n_out / qh >= 256) {      // few rows (decoding) of heads wide enough: 1024 threads a row
+    if (qh == 4) return pick_window_attn_talk<4, 1024>(a, R, row_seq, row_pos, ch, out, ldo, out_fp32, stream);
+    if (qh == 2) return pick_window_attn_talk<2, 1024>(a, R, row_seq, row_pos, ch, out, ldo, out_fp32, stream);
+    return pick_window_attn_talk<1, 1024>(a, R, row_seq, row_pos, ch, out, ldo, out_fp32, stream);
   }
-  if (n_out <= 512) return launch_window_attn_talk<2, 256>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
-  if (n_out <= 2048) return launch_window_attn_talk<8, 256>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
-  return launch_window_attn_talk<TALK_MAX_ACC, 256>(a, R, row_seq, row_pos, out, ldo, out_fp32, stream);
+  if (qh == 4) return pick_window_attn_talk<4, 256>(a, R, row_seq, row_pos, ch, out, ldo, out_fp32, stream);
+  if (qh == 2) return pick_window_attn_talk<2, 256>(a, R, row_seq, row_pos, ch, out, ldo, out_fp32, stream);
+  return pick_window_attn_talk<1, 256>(a, R, row_seq, row_pos, ch, out, ldo, out_fp32, stream);
+}
+
+// one-token steps (and any rows without chunk tables): a CTA per row
+extern "C" int lp_window_attn_talk(const lp_window_attn_desc* d, int R, const int* row_seq, const int* row_pos, void* out, long long ldo,
+                                   int out_fp32, void* stream_) {
+  return window_attn_talk(d, R, row_seq, row_pos, TalkChunks{0, nullptr, nullptr, nullptr}, out, ldo, out_fp32,
+                          reinterpret_cast<cudaStream_t>(stream_));
+}
+
+// prompts and portions: the rows come as chunks of consecutive rows of one request, and tiles of rows share the keys they read
+extern "C" int lp_window_attn_talk_tiles(const lp_window_attn_desc* d, int R, const int* row_seq, const int* row_pos, int n_chunks,
+                                         const int* chunk_seq, const int* chunk_row0, const int* chunk_len, void* out, long long ldo,
+                                         int out_fp32, void* stream_) {
+  LP_REQUIRE(n_chunks <= 0 || (chunk_seq != nullptr && chunk_row0 != nullptr && chunk_len != nullptr), "lp_window_attn_talk_tiles: null operand");
+  return window_attn_talk(d, R, row_seq, row_pos, TalkChunks{n_chunks > 0 ? n_chunks : 0, chunk_seq, chunk_row0, chunk_len}, out, ldo, out_fp32,
+                          reinterpret_cast<cudaStream_t>(stream_));
 }
 
 extern "C" int lp_window_attn_tiles(const lp_window_attn_desc* d, int R, const int* row_seq, const int* row_pos, int n_chunks,

@@ -694,9 +694,13 @@ class SeqLMEngine:
             rc = self.L.lp_window_attn_pool(C.byref(d), b.n, _lib.ptr(b.seq_row0), _lib.ptr(b.seq_pos0), new, st)
             self._check(rc, "lp_window_attn_pool")
         o = self._empty((b.R, m.heads * m.vdim), self.act)
-        if mixing:      # weights mixed over the heads (and the output gate): one kernel for prompts and one-token steps
+        if mixing and b.decode:      # weights mixed over the heads (and the output gate): a CTA per row
             rc = self.L.lp_window_attn_talk(C.byref(d), b.R, _lib.ptr(b.row_seq), _lib.ptr(b.row_pos), _lib.ptr(o), o.stride(0),
                                             int(o.dtype == F32), st)
+        elif mixing:      # the same kernel over tiles of consecutive rows, which share the keys they read
+            rc = self.L.lp_window_attn_talk_tiles(C.byref(d), b.R, _lib.ptr(b.row_seq), _lib.ptr(b.row_pos), b.n_chunks,
+                                                  _lib.ptr(b.chunk_seq), _lib.ptr(b.chunk_row0), _lib.ptr(b.chunk_len), _lib.ptr(o),
+                                                  o.stride(0), int(o.dtype == F32), st)
         elif b.decode:
             rc = self.L.lp_window_attn(C.byref(d), b.R, _lib.ptr(b.row_seq), _lib.ptr(b.row_pos), _lib.ptr(o), o.stride(0),
                                        int(o.dtype == F32), st)

@@ -46,6 +46,7 @@ LAYERS = {
     "attention, odd sizes, one key head": attention_layer(heads=3, kv_heads=1, dim=5, vdim=7, window=3),
     "attention, six heads a group": attention_layer(heads=6, kv_heads=1, dim=4, vdim=4, window=6),
     "attention, every head its own keys": attention_layer(heads=2, kv_heads=2, dim=8, vdim=8, window=20),
+    "attention, four and eight heads a group": attention_layer(heads=8, kv_heads=1, dim=4, vdim=3, window=7),
     "latent": latent_layer(),
     "latent, one head": latent_layer(heads=1, dim=6, vdim=3, q_rank=7, kv_rank=5, window=6),
     "latent + experts": latent_layer(heads=2, dim=4, vdim=4, q_rank=4, kv_rank=4, window=3, mlp=moe()),
@@ -60,13 +61,13 @@ def test_each_mechanism_alone(backend, name):
     """a one-layer model: the whole prompt in one step, and the same tokens with the last ones decoded through cache and state"""
     cfg = model([LAYERS[name]])
     w = O.random_weights(cfg, seed=3)
-    toks = _tokens(11, cfg["vocab"], seed=1)
+    toks = _tokens(9, cfg["vocab"], seed=1)
     res = []
     want = O.forward(cfg, w, toks, residuals=res)
     eng = make_engine(cfg, w, backend)
     taps = []
     eng.tap = lambda li, x: taps.append(x.clone())
-    got = eng.step([StepEntry("p", toks, _all(11))])
+    got = eng.step([StepEntry("p", toks, _all(9))])
     assert rel_err(taps[0], res[0]) < TOL["float32"]              # the residual stream after the layer
     assert float(_rows(got, want).max()) < 5 * TOL["float32"]
     eng.tap = None
@@ -79,7 +80,7 @@ def test_positions_shift_and_loop_vectors(backend):
     and the vector added before every pass of the loop"""
     cfg = model([mlstm_layer(), latent_layer()], loop=(1, 2, 3))
     w = O.random_weights(cfg, seed=4)
-    toks = _tokens(7, cfg["vocab"], seed=5)
+    toks = _tokens(5, cfg["vocab"], seed=5)
     want = O.forward(cfg, w, toks)
     for name in ("l0.shift", "l1.shift", "loop.step"):
         w2 = dict(w)
@@ -89,7 +90,7 @@ def test_positions_shift_and_loop_vectors(backend):
     res = []
     eng = make_engine(cfg, w, backend)
     eng.tap = lambda li, x: res.append(x.clone())
-    got = eng.step([StepEntry("p", toks, _all(7))])
+    got = eng.step([StepEntry("p", toks, _all(5))])
     assert len(res) == 4
     assert float(_rows(got, want).max()) < 5 * TOL["float32"]
     # the same request row by row: every step's shift reads the row that the step before left in the slot
@@ -103,16 +104,17 @@ def test_prompt_then_long_decoding(backend, dtype):
     """a prompt, then tokens one by one: past every window, over many page borders, the recurrent state carried through every step"""
     cfg = mixed_model()
     w = O.random_weights(cfg, seed=11)
-    toks = _tokens(22 if dtype == "float32" else 14, cfg["vocab"], seed=2)
+    long = backend[0] == "cuda"      # the emulator spends seconds a step
+    toks = _tokens(90 if long else 12 if dtype == "float32" else 7, cfg["vocab"], seed=2)
     want = O.forward(cfg, w, toks)
-    eng = make_engine(cfg, w, backend, dtype)
-    got = _prompt_then_decode(eng, toks, 7)
+    eng = make_engine(cfg, w, backend, dtype, max_tokens=96)
+    got = _prompt_then_decode(eng, toks, 21 if long else 3)
     assert rel_err(got, want) < TOL[dtype]
     if dtype == "float32":
         assert float(_rows(got, want).max()) < 5 * TOL[dtype]
 
 
-@pytest.mark.parametrize("cuts", [(2, 2, 3, 9, 2), (5, 13), (1, 2, 15)])
+@pytest.mark.parametrize("cuts", [(2, 2, 3, 2), (5, 6), (1, 2, 17)])
 def test_portions_of_a_prompt(backend, cuts):
     """a prompt fed in portions: windows that reach into earlier portions, states and shifted rows handed from portion to portion,
     portions longer than the recurrence's 16-token stage"""
@@ -133,7 +135,7 @@ def test_batch_of_unequal_requests_and_reuse(backend):
     pages and the slot that were given back (the pools are sized so that it must)"""
     cfg = mixed_model()
     w = O.random_weights(cfg, seed=13)
-    lens = {"a": (1, 3), "b": (9, 4), "c": (18, 2)}            # prompt length, decoded tokens
+    lens = {"a": (1, 2), "b": (5, 3), "c": (8, 1)}            # prompt length, decoded tokens
     toks = {k: _tokens(p + d, cfg["vocab"], seed=30 + i) for i, (k, (p, d)) in enumerate(lens.items())}
     want = {k: O.forward(cfg, w, toks[k]) for k in lens}
     eng = make_engine(cfg, w, backend, max_tokens=8, max_seqs=3)
@@ -142,7 +144,7 @@ def test_batch_of_unequal_requests_and_reuse(backend):
     for i, k in enumerate(lens):
         got[k].append(out[i:i + 1])
     live = list(lens)
-    for step in range(4):
+    for step in range(3):
         live = [k for k in live if step < lens[k][1]]
         out = eng.step([StepEntry(k, [toks[k][lens[k][0] + step]], [0]) for k in live])
         for i, k in enumerate(live):
@@ -155,8 +157,8 @@ def test_batch_of_unequal_requests_and_reuse(backend):
     c = eng.cache
     assert c.pages_in_use() == 0 and len(c.free_slots) == c.n_slots
     before = (c.n_slots, c.n_pages)
-    t2 = _tokens(15, cfg["vocab"], seed=77)
-    again = eng.step([StepEntry("a", t2, _all(15))])           # the name of an ended request, a used slot, used pages
+    t2 = _tokens(7, cfg["vocab"], seed=77)
+    again = eng.step([StepEntry("a", t2, _all(7))])           # the name of an ended request, a used slot, used pages
     assert float(_rows(again, O.forward(cfg, w, t2)).max()) < 5 * TOL["float32"]
     assert (c.n_slots, c.n_pages) == before
 
@@ -192,6 +194,30 @@ def test_edge_of_the_window(backend, kind, mode):
     assert sum(p >= 0 for p in eng.cache.get("r").pages) <= -(-size // 4) + 1      # only the window's pages are still held
 
 
+@pytest.mark.gpu
+def test_far_keys_among_hundreds():
+    """windows of hundreds of keys (several key tiles of the attention kernels, many pages), sharp softmaxes: the key at the far edge
+    of the window carries weight on many rows, in prompts cut into portions and in decoding, and the oracle with a window one token
+    off is told apart; the rows of a portion's tiles start and end at every offset against the window's edge"""
+    layers = [attention_layer(heads=8, kv_heads=2, dim=16, vdim=8, window=150, scale=2.5),
+              latent_layer(heads=4, dim=8, vdim=8, q_rank=12, kv_rank=16, window=131, scale=0.45)]
+    cfg = model(layers, width=24)
+    w = O.random_weights(cfg, seed=31)
+    toks = _tokens(330, cfg["vocab"], seed=32)
+    want = O.forward(cfg, w, toks)
+    for delta in (-1, 1):
+        off = _rows(O.forward(_one_off(cfg, delta), w, toks), want)
+        assert int((off[150:] > 200 * TOL["float32"]).sum()) >= 40
+    eng = make_engine(cfg, w, ("cuda", None), max_tokens=400, page_size=16)
+    got, at = [], 0
+    for n in (129, 2, 67, 101, 3):
+        got.append(eng.step([StepEntry("r", toks[at:at + n], _all(n))]))
+        at += n
+    for t in toks[at:]:
+        got.append(eng.step([StepEntry("r", [t], [0])]))
+    assert float(_rows(torch.cat(got, 0), want).max()) < 5 * TOL["float32"]
+
+
 def test_sink_and_head_mixing_are_there(backend):
     """left out, each would move the rows by far more than the tolerance: a sink of large weight, a mixing matrix far from the unit
     matrix (also negative entries), a gate"""
@@ -211,20 +237,20 @@ def test_sink_and_head_mixing_are_there(backend):
 
 
 def test_memory_of_the_recurrence(backend):
-    """mLSTM with forget gates near one keeps the first tokens: changing token 0 moves the last row of a 40-token sequence on the
+    """mLSTM with forget gates near one keeps the first tokens: changing token 0 moves the last row of a 36-token sequence on the
     oracle; the engine carries the state over three 16-token stages, two portions, decoding, and into a slot that was used before"""
     cfg = model([mlstm_layer(heads=2, dim=4, vdim=6, gate_cap=6.0)])
     w = O.random_weights(cfg, seed=23)
     w["l0.mix.f.b"] = torch.tensor([6.0, 5.0])
-    toks = _tokens(40, cfg["vocab"], seed=8)
+    toks = _tokens(36, cfg["vocab"], seed=8)
     want = O.forward(cfg, w, toks)
     other = O.forward(cfg, w, [(toks[0] + 1) % cfg["vocab"]] + toks[1:])
-    assert float(_rows(other[-1:], want[-1:])) > 50 * TOL["float32"]
+    assert float(_rows(other[-1:], want[-1:])) > 20 * TOL["float32"]
     eng = make_engine(cfg, w, backend, max_seqs=1)
     eng.step([StepEntry("old", _tokens(5, cfg["vocab"], seed=9), [])])
     eng.finish("old")                                          # its state stays in the slot; the next request must not see it
-    got = [eng.step([StepEntry("r", toks[:35], _all(35))]), eng.step([StepEntry("r", toks[35:38], _all(3))]),
-           eng.step([StepEntry("r", toks[38:39], [0])]), eng.step([StepEntry("r", toks[39:], [0])])]
+    got = [eng.step([StepEntry("r", toks[:33], _all(33))]), eng.step([StepEntry("r", toks[33:35], _all(2))]),
+           eng.step([StepEntry("r", toks[35:], [0])])]
     assert eng.cache.n_slots == 1
     assert float(_rows(torch.cat(got, 0), want).max()) < 5 * TOL["float32"]
 
@@ -236,22 +262,22 @@ def test_sizes_that_are_equal_or_one(backend, dtype):
     layers = [attention_layer(heads=1, kv_heads=1, dim=4, vdim=4, window=1, mlp=moe(experts=1, top=1, ff=2)),
               latent_layer(heads=1, dim=4, vdim=4, q_rank=4, kv_rank=4, window=1, mlp=moe(experts=4, top=4, ff=4)),
               mlstm_layer(heads=1, dim=4, vdim=4, gate_cap=1.0)]
-    toks = _tokens(9, 23, seed=10)
-    for loop in ((0, 3, 1), None, (2, 2, 5)):
+    toks = _tokens(6, 23, seed=10)
+    for loop in ((0, 3, 1), None, (2, 2, 5)) if dtype == "float32" else ((0, 3, 1),):
         cfg = model(layers, width=9, vocab=23, eps=1e-6, embed_scale=1.0, loop=loop)
         w = O.random_weights(cfg, seed=24)
         want = O.forward(cfg, w, toks)
         eng = make_engine(cfg, w, backend, dtype)
-        got = _prompt_then_decode(eng, toks, 4)
+        got = _prompt_then_decode(eng, toks, 3)
         assert rel_err(got, want) < TOL[dtype]
 
 
 def test_greedy_generation_through_the_scheduler(backend):
     cfg = mixed_model()
     w = O.random_weights(cfg, seed=19)
-    prompts = [_tokens(n, cfg["vocab"], seed=40 + n) for n in (3, 9, 1)]
+    prompts = [_tokens(n, cfg["vocab"], seed=40 + n) for n in (3, 6, 1)]
     eng = make_engine(cfg, w, backend, max_seqs=2)
-    outs = generate(eng, prompts, max_new_tokens=3)
+    outs = generate(eng, prompts, max_new_tokens=2)
     for p, o in zip(prompts, outs):
         seq = list(p)
         for t in o:                                   # every generated token is the oracle's arg-max given what came before
@@ -259,11 +285,11 @@ def test_greedy_generation_through_the_scheduler(backend):
             top2 = lg.topk(2).values
             assert int(lg.argmax()) == t or float(top2[0] - top2[1]) < 1e-3
             seq.append(t)
-        assert len(o) == 3
+        assert len(o) == 2
     assert eng.cache.pages_in_use() == 0
     sched = Scheduler(eng, max_running=1)
     first = outs[0][0]
-    sched.add(Request("x", prompts[0], max_new_tokens=3, eos={first}))
+    sched.add(Request("x", prompts[0], max_new_tokens=2, eos={first}))
     sched.add(Request("y", prompts[1], max_new_tokens=2))
     done = sched.run()
     assert done["x"].output == [first] and done["y"].output == outs[1][:2]
