@@ -985,7 +985,7 @@ static int launch_window_attn_talk(const WinArgs& a, int R, const int* row_seq, 
   while (tile < 256 && units * tile < NT && talk_smem_bytes(a.heads, a.dim, 2 * tile, RQ, red) <= 96 * 1024) tile *= 2;
   while (tile > 16 && talk_smem_bytes(a.heads, a.dim, tile, RQ, red) > 200 * 1024) tile /= 2;
   const size_t smem = talk_smem_bytes(a.heads, a.dim, tile, RQ, red);
-  if (RQ > 1 && smem > 100 * 1024) return 1;
+  if (RQ > 1 && smem > 112 * 1024) return 1;      // two CTAs a multiprocessor
   LP_REQUIRE(smem <= 200 * 1024, "lp_window_attn_talk: heads=%d dim=%d do not fit shared memory", a.heads, a.dim);
   static size_t have = 48 * 1024;
   if (smem > have) {
