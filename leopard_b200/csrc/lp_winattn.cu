@@ -708,6 +708,7 @@ __device__ __forceinline__ void talk_tile_scores(const WinArgs& a, const TalkRow
 #pragma unroll
       for (int h = 0; h < 4; ++h) sc[rq][h] = 0.f;
     if (vec) {
+#pragma unroll 4
       for (int d = 0; d < a.dim; d += 4) {
         const float4 k4 = *reinterpret_cast<const float4*>(kp + d);
 #pragma unroll
@@ -892,7 +893,7 @@ window_attn_talk_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const
         const int c = u % a.vdim, gq = u / a.vdim;      // gq = g * nqg + query group, so its first head is gq * QH
         const int off = v_base + (gq / nqg) * a.vdim + c;
         const float* wh = w_s + gq * QH;
-#pragma unroll 2
+#pragma unroll(RQ == 1 ? 8 : 4)      // that many value reads in flight per thread
         for (int jj = sl; jj < cnt; jj += slices) {
           const float v = row_s[jj][off];
 #pragma unroll
