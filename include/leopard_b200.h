@@ -582,7 +582,7 @@ int lp_parity_softmax(float* scores, long long ld, int Tq, int Tk, float scale, 
  * mechanisms are separate entry points with their constants as arguments, so that a model description (a list of layers) composes
  * them: csrc/lp_linear.cu, lp_stream32.cu, lp_seqmix.cu, lp_moe.cu.
  * ------------------------------------------------------------------------------------------------------------------ */
-enum lp_linear_epi { LP_EPI_NONE = 0, LP_EPI_XIELU = 1, LP_EPI_SILU_GATE = 2, LP_EPI_RELU2 = 3 };
+enum lp_linear_epi { LP_EPI_NONE = 0, LP_EPI_XIELU = 1, LP_EPI_SILU_GATE = 2, LP_EPI_RELU2 = 3, LP_EPI_CLAMP_GLU = 4 };
 enum lp_rot_layout { LP_ROT_HALF = 0, LP_ROT_INTERLEAVED = 1 };
 #define LP_RETENTION_CHUNK 32
 #define LP_LATENT_SPLIT_ROWS 16   /* lp_latent_attend: up to this many rows a CTA per (row, head) splits the keys over its warps */
@@ -590,7 +590,10 @@ enum lp_rot_layout { LP_ROT_HALF = 0, LP_ROT_INTERLEAVED = 1 };
 /* C[M, N'] = epi(A[M, K] W[N, K]^T), `batch` problems `*_batch` elements apart.  A: fp32 (a_fp32) or bf16; W: bf16; C: fp32 (c_fp32) or
  * bf16.  epi XIELU: a z^2 + z/2 (z > 0), b (exp(z) - 1 - z) + z/2 (z <= 0) with a = epi_a, b = epi_b.  epi SILU_GATE: W = [gate rows;
  * up rows], N' = N / 2, C = silu(gate) * up.  epi RELU2: max(z, 0)^2.  fp32 FMA accumulation in K order.  c_accum != 0: the result
- * is not stored but added, C <- C + c_scale * epi(...) (x <- x + m * sublayer(x) in the product's own store). */
+ * is not stored but added, C <- C + c_scale * epi(...) (x <- x + m * sublayer(x) in the product's own store).
+ * epi CLAMP_GLU: W = [gate rows; up rows], N' = N / 2, g = min(gate, epi_a), u = clamp(up, -epi_a, epi_a), C = g sigmoid(epi_b g) (u + 1).
+ * Before the epilogue an accumulator becomes row_scale[m] * acc + bias[n] (either may be NULL; m is the row of C, for lp_linear_pairs
+ * the pair; one problem only).  gate (fp32 [rows of C, ldg], or NULL): the epilogue's result is multiplied by sigmoid(gate[m, n]). */
 typedef struct lp_linear_desc {
   const void* A; long long lda; long long a_batch; int a_fp32;
   const void* W; long long ldw; long long w_batch;
@@ -598,6 +601,8 @@ typedef struct lp_linear_desc {
   int M, N, K, batch;
   int epi; float epi_a, epi_b;
   int c_accum; float c_scale;
+  const float* bias; const float* row_scale;
+  const float* gate; long long ldg;
 } lp_linear_desc;
 int lp_linear(const lp_linear_desc* desc, void* stream);
 /* row tiles of lp_linear_tile_rows() rows, each multiplied by the weight of group tile_group[tile] (w_batch elements apart; < 0: the
@@ -613,10 +618,32 @@ int lp_embed_rows_f32(const int* ids, int R, const void* table, long long ldt, i
 /* y = x / sqrt(mean(x^2) + eps) * gain_scalar (* gain_vec[c]); written to `out` (fp32 or bf16) or added to `accum` (fp32) */
 int lp_rmsnorm_f32(const float* x, long long ldx, int M, int D, float gain_scalar, const float* gain_vec, float eps, void* out,
                    long long ldo, int out_fp32, float* accum, long long ld_accum, void* stream);
-/* standalone activation for products that ran on lp_gemm_bf16: mode XIELU (N columns) or SILU_GATE (in has 2N columns: gate | up) */
+/* standalone activation for products that ran on lp_gemm_bf16: mode XIELU, RELU2 (N columns) or SILU_GATE, CLAMP_GLU (in has 2N
+ * columns: gate | up) */
 int lp_glu_f32(const void* in, long long ldi, int in_fp32, void* out, long long ldo, int out_fp32, int M, int N, int mode, float a,
                float b, void* stream);
+/* the same with every input of row m first multiplied by row_scale[m] (NULL: 1) */
+int lp_glu_scaled_f32(const void* in, long long ldi, int in_fp32, void* out, long long ldo, int out_fp32, int M, int N, int mode, float a,
+                      float b, const float* row_scale, void* stream);
+/* Dynamic Tanh, a norm without statistics: out = tanh(alpha x) * gain[c] + shift[c] (shift NULL: none).  With out2 the same rows are
+ * normed a second time with (alpha2, gain2, shift2) in the same pass (two sublayers that read the same stream). */
+int lp_dyt_f32(const float* x, long long ldx, int M, int D, float alpha, const float* gain, const float* shift, void* out, long long ldo,
+               float alpha2, const float* gain2, const float* shift2, void* out2, long long ldo2, int out_fp32, void* stream);
+/* y = x / sqrt(mean(x^2) + eps) * gain[c] * sigmoid(gate[m, c]) over fp32 rows (a norm over the concatenated heads of a mixer,
+ * followed by its output gate) */
+int lp_rmsnorm_gated_f32(const float* x, long long ldx, int M, int D, const float* gain, float eps, const float* gate, long long ldg,
+                         void* out, long long ldo, int out_fp32, void* stream);
+/* x <- x + mult * (y + y_bias[c]) * sigmoid(g[m, c] + g_bias[c]): a gated residual branch (biases NULL: none; g NULL: no gate) */
+int lp_gated_axpy_f32(float* x, long long ldx, const float* y, long long ldy, const float* y_bias, const float* g, long long ldg,
+                      const float* g_bias, float mult, int M, int N, void* stream);
+/* depth average: out = sum over j < n of coef[j] * hist[j] with hist fp32 [n][M, ldh] (layer_stride elements apart), coef fp32 [n] on the
+ * device; `copy` (NULL: none) receives the same rows (the buffer the next layer's branches are added to) */
+int lp_depth_average_f32(const float* hist, long long layer_stride, long long ldh, const float* coef, int n, float* out, long long ldo,
+                         float* copy, long long ldc, int M, int N, void* stream);
 
+/* what the retention kernels store: o / rms(o) per head * silu(g) (eps; the form of retention layers), or o itself (linear attention
+ * whose norm spans all heads: lp_rmsnorm_gated_f32 follows) */
+enum lp_retention_finish { LP_RET_FINISH_GATED_NORM = 0, LP_RET_FINISH_RAW = 1 };
 /* Retention over a packed batch.  qkvg fp32 [rows, ld] holds q | k (heads x dim) and v | g (heads x vdim) at the given column offsets.
  * state fp32 [slots][heads][dim][vdim] (slot_stride elements per slot).  out [rows, heads * vdim] fp32 or bf16. */
 typedef struct lp_retention_desc {
@@ -627,6 +654,8 @@ typedef struct lp_retention_desc {
   float k_scale, eps;
   float* state; long long slot_stride;
   void* out; long long ldo; int out_fp32;
+  int in_act;                               /* != 0: q, k and v are silu(projection) (only without rotation) */
+  int finish;                               /* lp_retention_finish */
 } lp_retention_desc;
 size_t lp_retention_workspace_bytes(int n_chunks, int heads, int dim, int vdim);
 /* Request s owns packed rows [seq_row0[s], seq_row0[s+1]), its first row is position seq_pos0[s], its state lives in slot seq_slot[s];
@@ -660,6 +689,8 @@ int lp_latent_attend(const lp_latent_desc* desc, int R, const int* row_seq, cons
 /* Grouped-query attention over a paged cache of rows [keys (kv_heads x dim) | values (kv_heads x vdim)] fp32, with the visibility
  * rules and score options of sliding-window designs as parameters (csrc/lp_winattn.cu).  Query at position i of a request sees
  *   - tokens j with 0 <= i - j < window (window <= 0: every j <= i),
+ *   - with chunk = C > 0 only those of them that lie in its own block of C positions, floor(j / C) = floor(i / C) (blocks are counted
+ *     from the request's position 0, wherever a prompt was cut),
  *   - the first keep_first tokens of the request, whatever their distance (they keep their own positions),
  *   - with pool = P > 0: one key / value per block of P tokens that lies wholly before the window (block b = positions bP .. bP+P-1
  *     is seen when bP + P - 1 <= i - window); they are the means of the block's cached key and value rows, kept in a second paged
@@ -685,6 +716,9 @@ typedef struct lp_window_attn_desc {
   int v_norm;                               /* != 0: every value head is divided by its root mean square (eps) and cached so */
   const float* talk;                        /* [heads, heads] fp32 or NULL: softmax weights mixed over the heads (lp_window_attn_talk) */
   int g_off;                                /* >= 0: column of an output gate in qkv, heads * vdim wide; out *= sigmoid(g) (lp_window_attn_talk) */
+  int chunk;                                /* > 0: block-local visibility (above) */
+  int kv_shared;                            /* != 0: `cache` is another layer's, already written for this step's rows: lp_window_attn_prep
+                                               prepares the queries only and qkv holds no keys or values */
 } lp_window_attn_desc;
 /* norm + rotation of the step's rows; keys and values go to the request's pages */
 int lp_window_attn_prep(const lp_window_attn_desc* desc, int R, const int* row_seq, const int* row_pos, void* stream);
@@ -767,9 +801,16 @@ int lp_moe_route(const void* h, long long ldh, int h_fp32, int T, int D, const v
  * weights = softmax over the chosen logits only */
 int lp_moe_route_softmax(const void* h, long long ldh, int h_fp32, int T, int D, const void* w_router, long long ldw, int E,
                          const float* logit_bias, int top, int* idx_out, float* w_out, void* stream);
+/* the plain sigmoid router: scores = sigmoid(W_router h), the `top` largest are chosen (ties to the lower index), weights = the chosen
+ * scores as they are */
+int lp_moe_route_sigmoid(const void* h, long long ldh, int h_fp32, int T, int D, const void* w_router, long long ldw, int E, int top,
+                         int* idx_out, float* w_out, void* stream);
+/* sorted[pair_row[i]] = w[i]: the pairs' weights in the row space of lp_moe_align (for products whose rows are scaled by them) */
+int lp_moe_sorted_weights(const int* pair_row, const float* w, int n_pairs, float* sorted, void* stream);
 int lp_moe_max_tiles(int n_pairs, int E, int tile_rows);
 int lp_moe_align(const int* idx, int n_pairs, int top, int E, int tile_rows, int max_tiles, int* tile_group, int* sorted_token,
                  int* pair_row, void* stream);
+/* w NULL: every pair counts once (its weight went into the expert's input) */
 int lp_moe_combine(const float* y, long long ldy, const int* pair_row, const float* w, int top, const float* shared, long long lds,
                    const float* gate, float* out, long long ldo, int T, int D, void* stream);
 

@@ -77,7 +77,9 @@ class ProfileRecord(C.Structure):
 
 _P = C.POINTER
 
-EPI_NONE, EPI_XIELU, EPI_SILU_GATE, EPI_RELU2 = 0, 1, 2, 3
+EPI_NONE, EPI_XIELU, EPI_SILU_GATE, EPI_RELU2, EPI_CLAMP_GLU = 0, 1, 2, 3, 4
+GATED_EPIS = (EPI_SILU_GATE, EPI_CLAMP_GLU)      # W = [gate rows; up rows], half as many output columns
+RET_FINISH_GATED_NORM, RET_FINISH_RAW = 0, 1
 QKNORM_NONE, QKNORM_HEAD, QKNORM_FULL = 0, 1, 2
 ROT_HALF, ROT_INTERLEAVED = 0, 1
 RETENTION_CHUNK = 32
@@ -87,7 +89,7 @@ class LinearDesc(C.Structure):
     """lp_linear_desc (include/leopard_b200.h)."""
     _fields_ = [("A", _vp), ("lda", _ll), ("a_batch", _ll), ("a_fp32", _i), ("W", _vp), ("ldw", _ll), ("w_batch", _ll), ("C", _vp),
                 ("ldc", _ll), ("c_batch", _ll), ("c_fp32", _i), ("M", _i), ("N", _i), ("K", _i), ("batch", _i), ("epi", _i),
-                ("epi_a", _f), ("epi_b", _f), ("c_accum", _i), ("c_scale", _f)]
+                ("epi_a", _f), ("epi_b", _f), ("c_accum", _i), ("c_scale", _f), ("bias", _vp), ("row_scale", _vp), ("gate", _vp), ("ldg", _ll)]
 
 
 class WindowAttnDesc(C.Structure):
@@ -97,7 +99,7 @@ class WindowAttnDesc(C.Structure):
                 ("rot_layout", _i), ("rot_mscale", _f), ("v_inv_freq", _vp), ("v_rot_dims", _i), ("v_rot_layout", _i), ("cache", _vp),
                 ("page_size", _i), ("page_table", _vp), ("max_pages", _i), ("pooled", _vp), ("pooled_table", _vp),
                 ("max_pooled_pages", _i), ("pool", _i), ("window", _i), ("keep_first", _i), ("scale", _f), ("softcap", _f), ("sink", _i),
-                ("q_bias", _vp), ("k_bias", _vp), ("v_bias", _vp), ("v_norm", _i), ("talk", _vp), ("g_off", _i)]
+                ("q_bias", _vp), ("k_bias", _vp), ("v_bias", _vp), ("v_norm", _i), ("talk", _vp), ("g_off", _i), ("chunk", _i), ("kv_shared", _i)]
 
 
 class MinGRUDesc(C.Structure):
@@ -110,7 +112,8 @@ class RetentionDesc(C.Structure):
     """lp_retention_desc (include/leopard_b200.h)."""
     _fields_ = [("qkvg", _vp), ("ld", _ll), ("q_off", _i), ("k_off", _i), ("v_off", _i), ("g_off", _i), ("heads", _i), ("dim", _i),
                 ("vdim", _i), ("decay", _vp), ("inv_freq", _vp), ("rot_dims", _i), ("rot_layout", _i), ("rot_mscale", _f),
-                ("k_scale", _f), ("eps", _f), ("state", _vp), ("slot_stride", _ll), ("out", _vp), ("ldo", _ll), ("out_fp32", _i)]
+                ("k_scale", _f), ("eps", _f), ("state", _vp), ("slot_stride", _ll), ("out", _vp), ("ldo", _ll), ("out_fp32", _i),
+                ("in_act", _i), ("finish", _i)]
 
 
 class LatentDesc(C.Structure):
@@ -236,6 +239,13 @@ _SIGS = {
     "lp_mingru_decode": (_i, [C.POINTER(MinGRUDesc), _i, _vp, _vp, _vp, _vp]),
     "lp_rmsnorm_f32": (_i, [_vp, _ll, _i, _i, _f, _vp, _f, _vp, _ll, _i, _vp, _ll, _vp]),
     "lp_glu_f32": (_i, [_vp, _ll, _i, _vp, _ll, _i, _i, _i, _i, _f, _f, _vp]),
+    "lp_glu_scaled_f32": (_i, [_vp, _ll, _i, _vp, _ll, _i, _i, _i, _i, _f, _f, _vp, _vp]),
+    "lp_dyt_f32": (_i, [_vp, _ll, _i, _i, _f, _vp, _vp, _vp, _ll, _f, _vp, _vp, _vp, _ll, _i, _vp]),
+    "lp_rmsnorm_gated_f32": (_i, [_vp, _ll, _i, _i, _vp, _f, _vp, _ll, _vp, _ll, _i, _vp]),
+    "lp_gated_axpy_f32": (_i, [_vp, _ll, _vp, _ll, _vp, _vp, _ll, _vp, _f, _i, _i, _vp]),
+    "lp_depth_average_f32": (_i, [_vp, _ll, _ll, _vp, _i, _vp, _ll, _vp, _ll, _i, _i, _vp]),
+    "lp_moe_route_sigmoid": (_i, [_vp, _ll, _i, _i, _i, _vp, _ll, _i, _i, _vp, _vp, _vp]),
+    "lp_moe_sorted_weights": (_i, [_vp, _vp, _i, _vp, _vp]),
     "lp_retention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "lp_retention_prefill": (_i, [C.POINTER(RetentionDesc), _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "lp_retention_decode": (_i, [C.POINTER(RetentionDesc), _i, _vp, _vp, _vp, _vp]),
@@ -292,7 +302,8 @@ STREAM32_SYMBOLS = ("lp_last_error", "lp_abi_version", "lp_launch_count", "lp_li
                     "lp_moe_combine", "lp_axpy_f32", "lp_window_attn_prep", "lp_window_attn_pool", "lp_window_attn", "lp_window_attn_tiles",
                     "lp_mingru_workspace_bytes",
                     "lp_mingru_prefill", "lp_mingru_decode", "lp_window_attn_talk", "lp_window_attn_talk_tiles", "lp_mlstm_workspace_bytes", "lp_mlstm",
-                    "lp_add_positions_f32", "lp_add_row_f32", "lp_token_shift_f32", "lp_moe_route_softmax")
+                    "lp_add_positions_f32", "lp_add_row_f32", "lp_token_shift_f32", "lp_moe_route_softmax", "lp_glu_scaled_f32", "lp_dyt_f32",
+                    "lp_rmsnorm_gated_f32", "lp_gated_axpy_f32", "lp_depth_average_f32", "lp_moe_route_sigmoid", "lp_moe_sorted_weights")
 STREAM32_OPTIONAL = ("lp_gemm_bf16",)      # present in the native libraries, absent from the CPU-emulated build
 _stream32 = None
 

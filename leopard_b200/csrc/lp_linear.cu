@@ -2,8 +2,12 @@
 //
 //   lp_linear          C[M,N] = epi(A[M,K] · W[N,K]^T): A fp32 or bf16, W bf16 (nn.Linear layout), C fp32 or bf16, accumulation in
 //                      fp32 FMAs in index order of K (no tensor-core rounding: with fp32 A this is a true 32-bit product, the bf16
-//                      weight is exact in fp32).  Epilogues: none, xIELU, squared relu, gated SiLU (W = [gate rows; up rows], C has
-//                      N/2 columns).  With c_accum the result is scaled and ADDED to C (the residual update of a pre-norm layer).
+//                      weight is exact in fp32).  Epilogues: none, xIELU, squared relu, gated SiLU and the clamped gated unit (W =
+//                      [gate rows; up rows], C has N/2 columns).  Before the epilogue every accumulator may be multiplied by a
+//                      number per output row (row_scale: a router weight that multiplies an expert's INPUT is the same as one
+//                      that multiplies its first products) and take a bias per weight row.  With c_accum the result is scaled
+//                      and ADDED to C (the residual update of a pre-norm layer); with `gate` it is first multiplied by
+//                      sigmoid(gate[m, n]) (a gated residual branch closes in the store of its last product).
 //                      `batch` independent problems with element strides (per-head products of latent attention).
 //                      Two kernels: a 64 x 64 x 16 shared-memory tile kernel (prefill), and a weight-streaming kernel with one warp
 //                      per output column for M <= 8 rows (decode: every weight byte is read once, 16-byte loads).
@@ -33,6 +37,9 @@ struct LinArgs {
   const int* tile_group;  // grouped: group of each row tile, or NULL
   const int* z_group;     // pairs (rows kernel): weight group of problem z, or NULL; problem z reads A row z / a_div and writes C row z
   int a_div;
+  const float* bias;      // [N] added to the accumulators before the epilogue, or NULL
+  const float* row_scale; // [rows of C] multiplies the accumulators before the bias, or NULL
+  const float* gate; long long ldg;   // [rows of C, N'] pre-activations: the result is multiplied by sigmoid(gate), or NULL
 };
 
 __device__ __forceinline__ float lin_load(const float* p) { return *p; }
@@ -60,6 +67,16 @@ __device__ __forceinline__ float lin_epi(int epi, float v, float e0, float e1) {
     return r * r;
   }
   return epi == LP_EPI_XIELU ? xielu_f(v, e0, e1) : v;
+}
+
+// the two gated units: silu(g) * u, and g' sigmoid(e1 g') (u' + 1) with g' = min(g, e0), u' = clamp(u, -e0, e0)
+__device__ __forceinline__ float lin_gate(int epi, float g, float u, float e0, float e1) {
+  if (epi == LP_EPI_CLAMP_GLU) {
+    g = fminf(g, e0);
+    u = fminf(fmaxf(u, -e0), e0);
+    return g / (1.0f + expf(-e1 * g)) * (u + 1.0f);
+  }
+  return silu32_f(g) * u;
 }
 
 // 64 x 64 output tile per CTA, 4 x 4 outputs per thread, K in steps of 16 through shared memory.  GATED: two accumulator sets, the
@@ -129,11 +146,18 @@ __global__ void __launch_bounds__(LIN_THREADS) linear_tile_kernel(LinArgs a) {
   for (int i = 0; i < 4; ++i) {
     const int m = m0 + tm + i;
     if (m >= a.M) continue;
+    const float rs = a.row_scale != nullptr ? a.row_scale[m] : 1.0f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tn + j;
       if (n >= n_out) continue;
-      float v = GATED ? silu32_f(acc[i][j]) * acc2[i][j] : lin_epi(a.epi, acc[i][j], a.e0, a.e1);
+      float z = acc[i][j] * rs, z2 = GATED ? acc2[i][j] * rs : 0.f;
+      if (a.bias != nullptr) {
+        z += a.bias[n];
+        if (GATED) z2 += a.bias[n + n_out];
+      }
+      float v = GATED ? lin_gate(a.epi, z, z2, a.e0, a.e1) : lin_epi(a.epi, z, a.e0, a.e1);
+      if (a.gate != nullptr) v /= 1.0f + expf(-a.gate[(long long)m * a.ldg + n]);
       if (a.c_accum) v = fmaf(a.c_scale, v, lin_load(C + (long long)m * a.ldc + n));
       lin_store(C + (long long)m * a.ldc + n, v);
     }
@@ -223,7 +247,17 @@ __global__ void __launch_bounds__(ROWS_WARPS * 32) linear_rows_kernel(LinArgs a)
         if (GATED) s2 += __shfl_xor_sync(0xffffffffu, s2, o);
       }
       if (lane == 0) {
-        float v = GATED ? silu32_f(s) * s2 : lin_epi(a.epi, s, a.e0, a.e1);
+        if (a.row_scale != nullptr) {
+          const float rs = a.row_scale[pairs ? z : m];
+          s *= rs;
+          s2 *= rs;
+        }
+        if (a.bias != nullptr) {
+          s += a.bias[n];
+          if (GATED) s2 += a.bias[n + n_out];
+        }
+        float v = GATED ? lin_gate(a.epi, s, s2, a.e0, a.e1) : lin_epi(a.epi, s, a.e0, a.e1);
+        if (a.gate != nullptr) v /= 1.0f + expf(-a.gate[(long long)(pairs ? z : m) * a.ldg + n]);
         if (a.c_accum) v = fmaf(a.c_scale, v, lin_load(C + (long long)m * a.ldc + n));
         lin_store(C + (long long)m * a.ldc + n, v);
       }
@@ -247,7 +281,7 @@ static int launch_linear(const LinArgs& a, int batch, int m_tiles, bool allow_ro
 }
 
 static int dispatch_linear(const LinArgs& a, int a_fp32, int c_fp32, int batch, int m_tiles, bool allow_rows, cudaStream_t stream) {
-  const bool gated = a.epi == LP_EPI_SILU_GATE;
+  const bool gated = a.epi == LP_EPI_SILU_GATE || a.epi == LP_EPI_CLAMP_GLU;
   if (a_fp32) {
     if (c_fp32) return gated ? launch_linear<float, float, true>(a, batch, m_tiles, allow_rows, stream)
                              : launch_linear<float, float, false>(a, batch, m_tiles, allow_rows, stream);
@@ -269,8 +303,8 @@ extern "C" int lp_linear(const lp_linear_desc* d, void* stream_) {
   LP_REQUIRE(d != nullptr && d->A != nullptr && d->W != nullptr && d->C != nullptr, "lp_linear: null operand");
   LP_REQUIRE(d->M >= 0 && d->N > 0 && d->K > 0 && d->batch >= 1, "lp_linear: bad problem M=%d N=%d K=%d batch=%d", d->M, d->N, d->K,
              d->batch);
-  LP_REQUIRE(d->epi >= LP_EPI_NONE && d->epi <= LP_EPI_RELU2, "lp_linear: bad epilogue %d", d->epi);
-  LP_REQUIRE(d->epi != LP_EPI_SILU_GATE || d->N % 2 == 0, "lp_linear: the gated epilogue needs an even N (gate rows, then up rows)");
+  LP_REQUIRE(d->epi >= LP_EPI_NONE && d->epi <= LP_EPI_CLAMP_GLU, "lp_linear: bad epilogue %d", d->epi);
+  LP_REQUIRE((d->epi != LP_EPI_SILU_GATE && d->epi != LP_EPI_CLAMP_GLU) || d->N % 2 == 0, "lp_linear: the gated epilogue needs an even N (gate rows, then up rows)");
   if (d->M == 0) return 0;
   LinArgs a;
   a.A = d->A; a.lda = d->lda; a.a_batch = d->a_batch;
@@ -279,6 +313,8 @@ extern "C" int lp_linear(const lp_linear_desc* d, void* stream_) {
   a.M = d->M; a.N = d->N; a.K = d->K;
   a.epi = d->epi; a.e0 = d->epi_a; a.e1 = d->epi_b; a.c_accum = d->c_accum; a.c_scale = d->c_scale;
   a.a_rows = nullptr; a.tile_group = nullptr; a.z_group = nullptr; a.a_div = 1;
+  a.bias = d->bias; a.row_scale = d->row_scale; a.gate = d->gate; a.ldg = d->ldg;
+  LP_REQUIRE(d->batch == 1 || (d->bias == nullptr && d->row_scale == nullptr), "lp_linear: bias and row scale are for one problem");
   return dispatch_linear(a, d->a_fp32, d->c_fp32, d->batch, (d->M + LIN_BM - 1) / LIN_BM, true, stream);
 }
 
@@ -289,8 +325,8 @@ extern "C" int lp_linear_pairs(const lp_linear_desc* d, const int* pair_group, i
   LP_REQUIRE(d != nullptr && d->A != nullptr && d->W != nullptr && d->C != nullptr && pair_group != nullptr, "lp_linear_pairs: null operand");
   LP_REQUIRE(d->N > 0 && d->K > 0 && a_div >= 1 && n_pairs >= 0 && n_pairs <= 65535, "lp_linear_pairs: bad problem N=%d K=%d pairs=%d", d->N,
              d->K, n_pairs);
-  LP_REQUIRE(d->epi >= LP_EPI_NONE && d->epi <= LP_EPI_RELU2, "lp_linear_pairs: bad epilogue %d", d->epi);
-  LP_REQUIRE(d->epi != LP_EPI_SILU_GATE || d->N % 2 == 0, "lp_linear_pairs: the gated epilogue needs an even N");
+  LP_REQUIRE(d->epi >= LP_EPI_NONE && d->epi <= LP_EPI_CLAMP_GLU, "lp_linear_pairs: bad epilogue %d", d->epi);
+  LP_REQUIRE((d->epi != LP_EPI_SILU_GATE && d->epi != LP_EPI_CLAMP_GLU) || d->N % 2 == 0, "lp_linear_pairs: the gated epilogue needs an even N");
   if (n_pairs == 0) return 0;
   LinArgs a;
   a.A = d->A; a.lda = d->lda; a.a_batch = 0;
@@ -299,6 +335,7 @@ extern "C" int lp_linear_pairs(const lp_linear_desc* d, const int* pair_group, i
   a.M = 1; a.N = d->N; a.K = d->K;
   a.epi = d->epi; a.e0 = d->epi_a; a.e1 = d->epi_b; a.c_accum = d->c_accum; a.c_scale = d->c_scale;
   a.a_rows = nullptr; a.tile_group = nullptr; a.z_group = pair_group; a.a_div = a_div;
+  a.bias = d->bias; a.row_scale = d->row_scale; a.gate = d->gate; a.ldg = d->ldg;
   return dispatch_linear(a, d->a_fp32, d->c_fp32, n_pairs, 1, true, stream);
 }
 
@@ -307,8 +344,8 @@ extern "C" int lp_linear_grouped(const lp_linear_desc* d, const int* tile_group,
   LP_REQUIRE(d != nullptr && d->A != nullptr && d->W != nullptr && d->C != nullptr && tile_group != nullptr,
              "lp_linear_grouped: null operand");
   LP_REQUIRE(d->N > 0 && d->K > 0 && n_tiles >= 0, "lp_linear_grouped: bad problem N=%d K=%d tiles=%d", d->N, d->K, n_tiles);
-  LP_REQUIRE(d->epi >= LP_EPI_NONE && d->epi <= LP_EPI_RELU2, "lp_linear_grouped: bad epilogue %d", d->epi);
-  LP_REQUIRE(d->epi != LP_EPI_SILU_GATE || d->N % 2 == 0, "lp_linear_grouped: the gated epilogue needs an even N");
+  LP_REQUIRE(d->epi >= LP_EPI_NONE && d->epi <= LP_EPI_CLAMP_GLU, "lp_linear_grouped: bad epilogue %d", d->epi);
+  LP_REQUIRE((d->epi != LP_EPI_SILU_GATE && d->epi != LP_EPI_CLAMP_GLU) || d->N % 2 == 0, "lp_linear_grouped: the gated epilogue needs an even N");
   if (n_tiles == 0) return 0;
   LinArgs a;
   a.A = d->A; a.lda = d->lda; a.a_batch = 0;
@@ -317,6 +354,7 @@ extern "C" int lp_linear_grouped(const lp_linear_desc* d, const int* tile_group,
   a.M = n_tiles * LIN_BM; a.N = d->N; a.K = d->K;
   a.epi = d->epi; a.e0 = d->epi_a; a.e1 = d->epi_b; a.c_accum = d->c_accum; a.c_scale = d->c_scale;
   a.a_rows = a_rows; a.tile_group = tile_group; a.z_group = nullptr; a.a_div = 1;
+  a.bias = d->bias; a.row_scale = d->row_scale; a.gate = d->gate; a.ldg = d->ldg;
   return dispatch_linear(a, d->a_fp32, d->c_fp32, 1, n_tiles, false, stream);
 }
 

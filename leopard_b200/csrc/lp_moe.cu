@@ -8,6 +8,9 @@
 //                    Optionally one more row of weights gives a per-token sigmoid gate (for a shared expert).
 //   lp_moe_route_softmax  the plain token-choice router on the same kernel: logits z = W_router h + bias, the `top` largest logits are
 //                    chosen (ties to the lower index), weights = softmax over the chosen logits only.
+//   lp_moe_route_sigmoid  the plain sigmoid router on the same kernel: the `top` largest scores sigmoid(z) are chosen and are the
+//                    weights as they are (for designs that multiply an expert's INPUT by its score: lp_moe_sorted_weights puts the
+//                    weights into the row space of lp_moe_align, the grouped products take them as row scales).
 //   lp_moe_align     sorts the (token, choice) pairs by expert into a row space where every expert's segment is padded to whole
 //                    64-row tiles (the tile of lp_linear_grouped): tile_group[tile] = expert or -1, sorted_token[row] = token or -1,
 //                    pair_row[token * top + k] = the pair's row.  Sizes stay on the device: no host synchronisation.
@@ -68,7 +71,7 @@ moe_route_kernel(const HT* __restrict__ h, long long ldh, int T, int D, const bf
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     const float s = 1.0f / (1.0f + expf(-acc));
     if (lane == 0) {
-      if (softmax_mode) {      // the logit itself is score and choice
+      if (softmax_mode == 1) {      // the logit itself is score and choice
         sc[e] = ch[e] = acc + (logit_bias != nullptr ? logit_bias[e] : 0.f);
       } else if (e < E) {
         sc[e] = s;
@@ -105,7 +108,7 @@ moe_route_kernel(const HT* __restrict__ h, long long ldh, int T, int D, const bf
       if (!kept[g])
         for (int i = 0; i < gs; ++i) ch[g * gs + i] = -INFINITY;
   }
-  if (softmax_mode) {
+  if (softmax_mode == 1) {
     float mx = -INFINITY, sum = 0.f;
     for (int k = 0; k < top; ++k) {
       int best = 0;
@@ -130,7 +133,14 @@ moe_route_kernel(const HT* __restrict__ h, long long ldh, int T, int D, const bf
     sum += sc[best];
     ch[best] = -INFINITY;   // taken; the host guarantees that the eligible experts outnumber `top`
   }
-  for (int k = 0; k < top; ++k) w_out[(long long)t * top + k] = sc[idx_out[(long long)t * top + k]] / (sum + 1e-20f);
+  // softmax_mode 2: the chosen scores as they are
+  for (int k = 0; k < top; ++k)
+    w_out[(long long)t * top + k] = sc[idx_out[(long long)t * top + k]] / (softmax_mode == 2 ? 1.0f : sum + 1e-20f);
+}
+
+__global__ void moe_sorted_weights_kernel(const int* __restrict__ pair_row, const float* __restrict__ w, int n_pairs, float* __restrict__ sorted) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_pairs) sorted[pair_row[i]] = w[i];
 }
 
 // one CTA: counts, padded offsets, scatter
@@ -172,7 +182,8 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, long long ldy, c
   if (t >= T) return;
   for (int c = threadIdx.x; c < D; c += blockDim.x) {
     float acc = 0.f;
-    for (int k = 0; k < top; ++k) acc = fmaf(w[(long long)t * top + k], y[(long long)pair_row[(long long)t * top + k] * ldy + c], acc);
+    for (int k = 0; k < top; ++k)
+      acc = fmaf(w != nullptr ? w[(long long)t * top + k] : 1.0f, y[(long long)pair_row[(long long)t * top + k] * ldy + c], acc);
     if (shared != nullptr) acc = fmaf(gate != nullptr ? gate[t] : 1.0f, shared[(long long)t * lds + c], acc);
     out[(long long)t * ldo + c] = acc;
   }
@@ -228,6 +239,35 @@ extern "C" int lp_moe_route_softmax(const void* h, long long ldh, int h_fp32, in
   return 0;
 }
 
+extern "C" int lp_moe_route_sigmoid(const void* h, long long ldh, int h_fp32, int T, int D, const void* w_router, long long ldw, int E,
+                                    int top, int* idx_out, float* w_out, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(h != nullptr && w_router != nullptr && idx_out != nullptr && w_out != nullptr, "lp_moe_route_sigmoid: null operand");
+  LP_REQUIRE(E > 0 && E <= MOE_MAX_EXPERTS && top > 0 && top <= E, "lp_moe_route_sigmoid: experts=%d top=%d (at most %d experts)", E, top,
+             MOE_MAX_EXPERTS);
+  if (T <= 0) return 0;
+  const unsigned grid = (unsigned)T;
+  if (h_fp32)
+    moe_route_kernel<float><<<grid, ROUTE_WARPS * 32, 0, stream>>>(reinterpret_cast<const float*>(h), ldh, T, D,
+        reinterpret_cast<const bf16*>(w_router), ldw, E, nullptr, 1, 1, top, nullptr, idx_out, w_out, nullptr, 2, nullptr);
+  else
+    moe_route_kernel<bf16><<<grid, ROUTE_WARPS * 32, 0, stream>>>(reinterpret_cast<const bf16*>(h), ldh, T, D,
+        reinterpret_cast<const bf16*>(w_router), ldw, E, nullptr, 1, 1, top, nullptr, idx_out, w_out, nullptr, 2, nullptr);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_moe_sorted_weights(const int* pair_row, const float* w, int n_pairs, float* sorted, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(pair_row != nullptr && w != nullptr && sorted != nullptr, "lp_moe_sorted_weights: null operand");
+  if (n_pairs <= 0) return 0;
+  moe_sorted_weights_kernel<<<(n_pairs + 255) / 256, 256, 0, stream>>>(pair_row, w, n_pairs, sorted);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
 extern "C" int lp_moe_max_tiles(int n_pairs, int E, int tile_rows) {
   const int full = (n_pairs + tile_rows - 1) / tile_rows + E;
   return full < n_pairs ? full : n_pairs;
@@ -249,7 +289,7 @@ extern "C" int lp_moe_align(const int* idx, int n_pairs, int top, int E, int til
 extern "C" int lp_moe_combine(const float* y, long long ldy, const int* pair_row, const float* w, int top, const float* shared,
                               long long lds, const float* gate, float* out, long long ldo, int T, int D, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  LP_REQUIRE(y != nullptr && pair_row != nullptr && w != nullptr && out != nullptr, "lp_moe_combine: null operand");
+  LP_REQUIRE(y != nullptr && pair_row != nullptr && out != nullptr, "lp_moe_combine: null operand");
   if (T <= 0) return 0;
   moe_combine_kernel<<<T, 128, 0, stream>>>(y, ldy, pair_row, w, top, shared, lds, gate, out, ldo, T, D);
   note_launch();

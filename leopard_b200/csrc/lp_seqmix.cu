@@ -5,7 +5,10 @@
 //                        YaRN's are built on the host: the kernels take the table and the factor).  Only the first `rot_dims` dimensions
 //                        of a head are rotated.
 //   Retention            per head S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t (no softmax, no denominator), then o / rms(o) per head
-//                        and an output gate silu(g).  State [slot][head][dim][vdim] fp32, carried between steps.
+//                        and an output gate silu(g).  State [slot][head][dim][vdim] fp32, carried between steps.  Two options make
+//                        it the linear ("lightning") attention of other designs: in_act = 1 applies silu to q, k and v as they
+//                        are read, and finish = LP_RET_FINISH_RAW stores o itself (the norm over all heads and the gate follow
+//                        in lp_rmsnorm_gated_f32).
 //       prefill          chunks of 32 tokens, three kernels: (1) every chunk's own contribution sum_j decay^(len-1-j) k_j v_j^T in
 //                        parallel, (2) a scan over the chunks of a request that turns them into the state at each chunk's start and
 //                        stores the final state, (3) every chunk's outputs in parallel: decay^(i+1) q_i^T S_start plus the causal
@@ -62,7 +65,16 @@ struct RetArgs {
   float k_scale, eps;
   float* state; long long slot_stride;
   void* out; long long ldo; int out_fp32;
+  int in_act, finish;
 };
+
+__device__ __forceinline__ float ret_silu(float z) { return z / (1.0f + expf(-z)); }
+// element d of one head's q or k: activation (when asked for), then rotation
+__device__ __forceinline__ float ret_qk(const RetArgs& a, const float* __restrict__ x, int d, int pos) {
+  if (a.in_act) return ret_silu(x[d]);      // the host admits an activation only without rotation
+  return rot_elem(x, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos);
+}
+__device__ __forceinline__ float ret_v(const RetArgs& a, float v) { return a.in_act ? ret_silu(v) : v; }
 
 // (1) U[chunk][head] = sum_j decay^(len-1-j) k_j v_j^T.  4 x 4 outputs per thread; a thread's four columns are vdim/4 apart, so that
 // the threads of a warp read consecutive shared-memory words.
@@ -82,13 +94,13 @@ retention_chunk_state_kernel(RetArgs a, const int* __restrict__ chunk_seq, const
     float v = 0.f;
     if (d < a.dim) {
       const float* kr = a.qkvg + (long long)(row0 + j) * a.ld + a.k_off + h * a.dim;
-      v = rot_elem(kr, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos0 + j) * a.k_scale * powf(dec, (float)(len - 1 - j));
+      v = ret_qk(a, kr, d, pos0 + j) * a.k_scale * powf(dec, (float)(len - 1 - j));
     }
     kd[i] = v;
   }
   for (int i = tid; i < len * vdimp; i += blockDim.x) {
     const int j = i / vdimp, d = i % vdimp;
-    vv[i] = d < a.vdim ? a.qkvg[(long long)(row0 + j) * a.ld + a.v_off + h * a.vdim + d] : 0.f;
+    vv[i] = d < a.vdim ? ret_v(a, a.qkvg[(long long)(row0 + j) * a.ld + a.v_off + h * a.vdim + d]) : 0.f;
   }
   __syncthreads();
   float* U = ws + ((long long)c * a.heads + h) * a.dim * a.vdim;
@@ -179,15 +191,15 @@ retention_chunk_out_kernel(RetArgs a, const int* __restrict__ chunk_seq, const i
     float qv = 0.f, kv = 0.f;
     if (j < len && d < a.dim) {
       const float* base = a.qkvg + (long long)(row0 + j) * a.ld + h * a.dim;
-      qv = rot_elem(base + a.q_off, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos0 + j);
-      kv = rot_elem(base + a.k_off, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos0 + j) * a.k_scale;
+      qv = ret_qk(a, base + a.q_off, d, pos0 + j);
+      kv = ret_qk(a, base + a.k_off, d, pos0 + j) * a.k_scale;
     }
     qs[i] = qv;
     ks[i] = kv;
   }
   for (int i = tid; i < RET_CHUNK * vdimp; i += blockDim.x) {
     const int j = i / vdimp, d = i % vdimp;
-    vv[i] = (j < len && d < a.vdim) ? a.qkvg[(long long)(row0 + j) * a.ld + a.v_off + h * a.vdim + d] : 0.f;
+    vv[i] = (j < len && d < a.vdim) ? ret_v(a, a.qkvg[(long long)(row0 + j) * a.ld + a.v_off + h * a.vdim + d]) : 0.f;
   }
   const float* S = ws + ((long long)c * a.heads + h) * a.dim * a.vdim;
   if (stage_s)
@@ -271,6 +283,15 @@ retention_chunk_out_kernel(RetArgs a, const int* __restrict__ chunk_seq, const i
       for (int q = 0; q < 4; ++q) os[(i0 + p) * vdimp + ty + q * tiles_y] = acc[p][q];
   }
   __syncthreads();
+  if (a.finish == LP_RET_FINISH_RAW) {      // o itself: what follows it is another kernel's
+    for (int e = tid; e < len * a.vdim; e += blockDim.x) {
+      const int i = e / a.vdim, y = e % a.vdim;
+      const long long o = (long long)(row0 + i) * a.ldo + h * a.vdim + y;
+      if (a.out_fp32) reinterpret_cast<float*>(a.out)[o] = os[i * vdimp + y];
+      else reinterpret_cast<bf16*>(a.out)[o] = __float2bfloat16(os[i * vdimp + y]);
+    }
+    return;
+  }
   // one warp per row: root mean square over the head's vdim outputs
   const int warp = tid >> 5, lane = tid & 31, nwarp = blockDim.x >> 5;
   for (int i = warp; i < len; i += nwarp) {
@@ -306,10 +327,10 @@ retention_decode_kernel(RetArgs a, const int* __restrict__ seq_row0, const int* 
   __shared__ float red[RET_DEC_THREADS / 32];
   const float* base = a.qkvg + (long long)row * a.ld;
   for (int d = tid; d < a.dim; d += blockDim.x) {
-    qs[d] = rot_elem(base + a.q_off + h * a.dim, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos);
-    ks[d] = rot_elem(base + a.k_off + h * a.dim, d, a.rot_dims, a.rot_layout, a.inv_freq, a.rot_mscale, pos) * a.k_scale;
+    qs[d] = ret_qk(a, base + a.q_off + h * a.dim, d, pos);
+    ks[d] = ret_qk(a, base + a.k_off + h * a.dim, d, pos) * a.k_scale;
   }
-  for (int y = tid; y < a.vdim; y += blockDim.x) vv[y] = base[a.v_off + h * a.vdim + y];
+  for (int y = tid; y < a.vdim; y += blockDim.x) vv[y] = ret_v(a, base[a.v_off + h * a.vdim + y]);
   __syncthreads();
   const float dec = a.decay[h];
   const bool fresh = pos == 0;
@@ -347,8 +368,11 @@ retention_decode_kernel(RetArgs a, const int* __restrict__ seq_row0, const int* 
   for (int w = 0; w < RET_DEC_THREADS / 32; ++w) tot += red[w];
   const float r = 1.0f / sqrtf(tot / (float)a.vdim + a.eps);
   for (int y = tid; y < a.vdim; y += blockDim.x) {
-    const float gt = base[a.g_off + h * a.vdim + y];
-    const float v = os[y] * r * (gt / (1.0f + expf(-gt)));
+    float v = os[y];
+    if (a.finish != LP_RET_FINISH_RAW) {
+      const float gt = base[a.g_off + h * a.vdim + y];
+      v = v * r * (gt / (1.0f + expf(-gt)));
+    }
     const long long o = (long long)row * a.ldo + h * a.vdim + y;
     if (a.out_fp32) reinterpret_cast<float*>(a.out)[o] = v;
     else reinterpret_cast<bf16*>(a.out)[o] = __float2bfloat16(v);
@@ -601,6 +625,9 @@ static int fill_ret(RetArgs& a, const lp_retention_desc* d) {
   a.decay = d->decay;
   a.inv_freq = d->inv_freq; a.rot_dims = d->rot_dims; a.rot_layout = d->rot_layout; a.rot_mscale = d->rot_mscale;
   a.k_scale = d->k_scale; a.eps = d->eps;
+  a.in_act = d->in_act; a.finish = d->finish;
+  LP_REQUIRE(d->in_act == 0 || d->rot_dims == 0, "lp_retention: an input activation together with rotation is not supported");
+  LP_REQUIRE(d->finish == LP_RET_FINISH_GATED_NORM || d->finish == LP_RET_FINISH_RAW, "lp_retention: bad finish %d", d->finish);
   a.state = d->state; a.slot_stride = d->slot_stride;
   a.out = d->out; a.ldo = d->ldo; a.out_fp32 = d->out_fp32;
   return 0;

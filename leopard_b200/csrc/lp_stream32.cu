@@ -12,6 +12,12 @@
 //   lp_token_shift_f32  y_t = h_t + (h_(t-1) - h_t) * mu per channel, with h the rows as they came in; the row before a request's
 //                       first row of this step comes from the request's slot (zeros at position 0), and the slot then takes the
 //                       request's last row.
+//   lp_dyt_f32          Dynamic Tanh: tanh(alpha x) * gain + shift per element, no statistics; one pass can serve the two sublayers of a
+//                       parallel layer (two parameter sets, two outputs).
+//   lp_rmsnorm_gated_f32  the RMS norm with a vector gain, multiplied by sigmoid(gate) per element (norm over a mixer's concatenated
+//                       heads and its output gate in one pass).
+//   lp_gated_axpy_f32   x <- x + mult (y + y_bias) sigmoid(g + g_bias): a residual branch behind a learned gate.
+//   lp_depth_average_f32  out = sum_j coef[j] X_j over the results of all layers so far (and a copy of it for the next layer's branches).
 //
 // One warp per row, statistics and normalisation in fp32; the row is read twice (the second read hits L1 / L2).
 #include "lp_host.h"
@@ -58,25 +64,92 @@ rmsnorm_f32_kernel(const float* __restrict__ x, long long ldx, int M, int D, flo
   }
 }
 
+template <typename OT>
+__global__ void __launch_bounds__(NORM32_WARPS * 32)
+rmsnorm_gated_f32_kernel(const float* __restrict__ x, long long ldx, int M, int D, const float* __restrict__ gain, float eps,
+                         const float* __restrict__ gate, long long ldg, OT* __restrict__ out, long long ldo) {
+  const int row = blockIdx.x * NORM32_WARPS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const float* xr = x + (long long)row * ldx;
+  float ss = 0.f;
+  for (int c = lane; c < D; c += 32) {
+    const float v = xr[c];
+    ss = fmaf(v, v, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float r = 1.0f / sqrtf(ss / (float)D + eps);
+  for (int c = lane; c < D; c += 32) {
+    float v = xr[c] * r;
+    if (gain != nullptr) v *= gain[c];
+    v /= 1.0f + expf(-gate[(long long)row * ldg + c]);
+    if constexpr (sizeof(OT) == 4) out[(long long)row * ldo + c] = v;
+    else out[(long long)row * ldo + c] = __float2bfloat16(v);
+  }
+}
+
 template <typename T> __device__ __forceinline__ float ld32(const T* p);
 template <> __device__ __forceinline__ float ld32<float>(const float* p) { return *p; }
 template <> __device__ __forceinline__ float ld32<bf16>(const bf16* p) { return __bfloat162float(*p); }
 __device__ __forceinline__ void st32(float* p, float v) { *p = v; }
 __device__ __forceinline__ void st32(bf16* p, float v) { *p = __float2bfloat16(v); }
 
-// mode LP_EPI_XIELU: out[m, n] = xielu(in[m, n]); LP_EPI_SILU_GATE: out[m, n] = silu(in[m, n]) * in[m, n + N]
+// mode LP_EPI_XIELU: out[m, n] = xielu(in[m, n]); LP_EPI_SILU_GATE: out[m, n] = silu(in[m, n]) * in[m, n + N]; LP_EPI_CLAMP_GLU: the
+// clamped gated unit of lp_linear on (in[m, n], in[m, n + N]) with limit a and slope b.  row_scale multiplies what is read.
 template <typename IT, typename OT>
 __global__ void glu_kernel(const IT* __restrict__ in, long long ldi, OT* __restrict__ out, long long ldo, int M, int N, int mode, float a,
-                           float b) {
+                           float b, const float* __restrict__ row_scale) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)M * N) return;
   const int m = (int)(i / N), n = (int)(i % N);
-  const float z = ld32<IT>(in + (long long)m * ldi + n);
+  const float rs = row_scale != nullptr ? row_scale[m] : 1.0f;
+  const float z = ld32<IT>(in + (long long)m * ldi + n) * rs;
   float v;
-  if (mode == LP_EPI_SILU_GATE) v = z / (1.0f + expf(-z)) * ld32<IT>(in + (long long)m * ldi + n + N);
+  if (mode == LP_EPI_SILU_GATE) v = z / (1.0f + expf(-z)) * (ld32<IT>(in + (long long)m * ldi + n + N) * rs);
+  else if (mode == LP_EPI_CLAMP_GLU) {
+    const float g = fminf(z, a), u = fminf(fmaxf(ld32<IT>(in + (long long)m * ldi + n + N) * rs, -a), a);
+    v = g / (1.0f + expf(-b * g)) * (u + 1.0f);
+  }
   else if (mode == LP_EPI_RELU2) v = fmaxf(z, 0.f) * fmaxf(z, 0.f);
   else v = z > 0.f ? a * z * z + 0.5f * z : b * (expm1f(z) - z) + 0.5f * z;
   st32(out + (long long)m * ldo + n, v);
+}
+
+template <typename OT>
+__global__ void dyt_f32_kernel(const float* __restrict__ x, long long ldx, int M, int D, float alpha, const float* __restrict__ gain,
+                               const float* __restrict__ shift, OT* __restrict__ out, long long ldo, float alpha2,
+                               const float* __restrict__ gain2, const float* __restrict__ shift2, OT* __restrict__ out2, long long ldo2) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)M * D) return;
+  const int m = (int)(i / D), c = (int)(i % D);
+  const float v = x[(long long)m * ldx + c];
+  st32(out + (long long)m * ldo + c, fmaf(tanhf(alpha * v), gain[c], shift != nullptr ? shift[c] : 0.f));
+  if (out2 != nullptr) st32(out2 + (long long)m * ldo2 + c, fmaf(tanhf(alpha2 * v), gain2[c], shift2 != nullptr ? shift2[c] : 0.f));
+}
+
+__global__ void gated_axpy_f32_kernel(float* __restrict__ x, long long ldx, const float* __restrict__ y, long long ldy,
+                                      const float* __restrict__ y_bias, const float* __restrict__ g, long long ldg,
+                                      const float* __restrict__ g_bias, float mult, int M, int N) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)M * N) return;
+  const int m = (int)(i / N), n = (int)(i % N);
+  float v = y[(long long)m * ldy + n] + (y_bias != nullptr ? y_bias[n] : 0.f);
+  if (g != nullptr) v /= 1.0f + expf(-(g[(long long)m * ldg + n] + (g_bias != nullptr ? g_bias[n] : 0.f)));
+  x[(long long)m * ldx + n] = fmaf(mult, v, x[(long long)m * ldx + n]);
+}
+
+__global__ void depth_average_f32_kernel(const float* __restrict__ hist, long long layer_stride, long long ldh,
+                                         const float* __restrict__ coef, int n, float* __restrict__ out, long long ldo,
+                                         float* __restrict__ copy, long long ldc, int M, int N) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)M * N) return;
+  const int m = (int)(i / N), c = (int)(i % N);
+  const float* src = hist + (long long)m * ldh + c;
+  float acc = 0.f;
+  for (int j = 0; j < n; ++j) acc = fmaf(coef[j], src[(long long)j * layer_stride], acc);
+  out[(long long)m * ldo + c] = acc;
+  if (copy != nullptr) copy[(long long)m * ldc + c] = acc;
 }
 
 __global__ void axpy_f32_kernel(float* __restrict__ y, long long ldy, const float* __restrict__ x, long long ldx, float alpha, int M, int N) {
@@ -208,19 +281,82 @@ extern "C" int lp_rmsnorm_f32(const float* x, long long ldx, int M, int D, float
 
 extern "C" int lp_glu_f32(const void* in, long long ldi, int in_fp32, void* out, long long ldo, int out_fp32, int M, int N, int mode,
                           float a, float b, void* stream_) {
+  return lp_glu_scaled_f32(in, ldi, in_fp32, out, ldo, out_fp32, M, N, mode, a, b, nullptr, stream_);
+}
+
+extern "C" int lp_glu_scaled_f32(const void* in, long long ldi, int in_fp32, void* out, long long ldo, int out_fp32, int M, int N, int mode,
+                                 float a, float b, const float* row_scale, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LP_REQUIRE(in != nullptr && out != nullptr && M >= 0 && N > 0, "lp_glu_f32: bad arguments");
-  LP_REQUIRE(mode == LP_EPI_XIELU || mode == LP_EPI_SILU_GATE || mode == LP_EPI_RELU2, "lp_glu_f32: mode %d is not an activation", mode);
+  LP_REQUIRE(mode == LP_EPI_XIELU || mode == LP_EPI_SILU_GATE || mode == LP_EPI_RELU2 || mode == LP_EPI_CLAMP_GLU,
+             "lp_glu_f32: mode %d is not an activation", mode);
   if (M == 0) return 0;
   const unsigned grid = (unsigned)(((long long)M * N + 255) / 256);
   if (in_fp32 && out_fp32)
-    glu_kernel<float, float><<<grid, 256, 0, stream>>>(reinterpret_cast<const float*>(in), ldi, reinterpret_cast<float*>(out), ldo, M, N, mode, a, b);
+    glu_kernel<float, float><<<grid, 256, 0, stream>>>(reinterpret_cast<const float*>(in), ldi, reinterpret_cast<float*>(out), ldo, M, N, mode, a, b, row_scale);
   else if (in_fp32)
-    glu_kernel<float, bf16><<<grid, 256, 0, stream>>>(reinterpret_cast<const float*>(in), ldi, reinterpret_cast<bf16*>(out), ldo, M, N, mode, a, b);
+    glu_kernel<float, bf16><<<grid, 256, 0, stream>>>(reinterpret_cast<const float*>(in), ldi, reinterpret_cast<bf16*>(out), ldo, M, N, mode, a, b, row_scale);
   else if (out_fp32)
-    glu_kernel<bf16, float><<<grid, 256, 0, stream>>>(reinterpret_cast<const bf16*>(in), ldi, reinterpret_cast<float*>(out), ldo, M, N, mode, a, b);
+    glu_kernel<bf16, float><<<grid, 256, 0, stream>>>(reinterpret_cast<const bf16*>(in), ldi, reinterpret_cast<float*>(out), ldo, M, N, mode, a, b, row_scale);
   else
-    glu_kernel<bf16, bf16><<<grid, 256, 0, stream>>>(reinterpret_cast<const bf16*>(in), ldi, reinterpret_cast<bf16*>(out), ldo, M, N, mode, a, b);
+    glu_kernel<bf16, bf16><<<grid, 256, 0, stream>>>(reinterpret_cast<const bf16*>(in), ldi, reinterpret_cast<bf16*>(out), ldo, M, N, mode, a, b, row_scale);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_dyt_f32(const float* x, long long ldx, int M, int D, float alpha, const float* gain, const float* shift, void* out,
+                          long long ldo, float alpha2, const float* gain2, const float* shift2, void* out2, long long ldo2, int out_fp32,
+                          void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(x != nullptr && gain != nullptr && out != nullptr && M >= 0 && D > 0, "lp_dyt_f32: bad arguments");
+  LP_REQUIRE(out2 == nullptr || gain2 != nullptr, "lp_dyt_f32: a second output without its gain");
+  if (M == 0) return 0;
+  const unsigned grid = (unsigned)(((long long)M * D + 255) / 256);
+  if (out_fp32)
+    dyt_f32_kernel<float><<<grid, 256, 0, stream>>>(x, ldx, M, D, alpha, gain, shift, reinterpret_cast<float*>(out), ldo, alpha2, gain2, shift2,
+                                                    reinterpret_cast<float*>(out2), ldo2);
+  else
+    dyt_f32_kernel<bf16><<<grid, 256, 0, stream>>>(x, ldx, M, D, alpha, gain, shift, reinterpret_cast<bf16*>(out), ldo, alpha2, gain2, shift2,
+                                                   reinterpret_cast<bf16*>(out2), ldo2);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_rmsnorm_gated_f32(const float* x, long long ldx, int M, int D, const float* gain, float eps, const float* gate,
+                                    long long ldg, void* out, long long ldo, int out_fp32, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(x != nullptr && gate != nullptr && out != nullptr && M >= 0 && D > 0, "lp_rmsnorm_gated_f32: bad arguments");
+  if (M == 0) return 0;
+  const unsigned grid = (unsigned)((M + NORM32_WARPS - 1) / NORM32_WARPS);
+  if (out_fp32)
+    rmsnorm_gated_f32_kernel<float><<<grid, NORM32_WARPS * 32, 0, stream>>>(x, ldx, M, D, gain, eps, gate, ldg, reinterpret_cast<float*>(out), ldo);
+  else
+    rmsnorm_gated_f32_kernel<bf16><<<grid, NORM32_WARPS * 32, 0, stream>>>(x, ldx, M, D, gain, eps, gate, ldg, reinterpret_cast<bf16*>(out), ldo);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_gated_axpy_f32(float* x, long long ldx, const float* y, long long ldy, const float* y_bias, const float* g, long long ldg,
+                                 const float* g_bias, float mult, int M, int N, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(x != nullptr && y != nullptr && M >= 0 && N > 0, "lp_gated_axpy_f32: bad arguments");
+  if (M == 0) return 0;
+  gated_axpy_f32_kernel<<<(unsigned)(((long long)M * N + 255) / 256), 256, 0, stream>>>(x, ldx, y, ldy, y_bias, g, ldg, g_bias, mult, M, N);
+  note_launch();
+  LP_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int lp_depth_average_f32(const float* hist, long long layer_stride, long long ldh, const float* coef, int n, float* out,
+                                    long long ldo, float* copy, long long ldc, int M, int N, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LP_REQUIRE(hist != nullptr && coef != nullptr && out != nullptr && n > 0 && M >= 0 && N > 0, "lp_depth_average_f32: bad arguments");
+  if (M == 0) return 0;
+  depth_average_f32_kernel<<<(unsigned)(((long long)M * N + 255) / 256), 256, 0, stream>>>(hist, layer_stride, ldh, coef, n, out, ldo, copy,
+                                                                                         ldc, M, N);
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -46,6 +46,7 @@ struct WinArgs {
   float scale, softcap; int sink;
   const float* q_bias; const float* k_bias; const float* v_bias; int v_norm;
   const float* talk; int g_off;
+  int chunk, kv_shared;
 };
 
 __device__ __forceinline__ float* win_token_row(const WinArgs& a, int seq, int pos) {
@@ -75,6 +76,7 @@ struct WinVisible {
 __device__ __forceinline__ WinVisible win_visible(const WinArgs& a, int pos) {
   WinVisible v;
   v.lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+  if (a.chunk > 0 && (pos / a.chunk) * a.chunk > v.lo) v.lo = (pos / a.chunk) * a.chunk;      // nothing before the query's own block
   v.n_keep = a.keep_first < v.lo ? a.keep_first : v.lo;
   if (v.n_keep < 0) v.n_keep = 0;
   v.n_blocks = (a.pool > 0 && a.window > 0 && pos - a.window + 1 > 0) ? (pos - a.window + 1) / a.pool : 0;
@@ -97,19 +99,20 @@ window_attn_prep_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, n_warps = blockDim.x >> 5;
   const int seq = row_seq[r], pos = row_pos[r];
   float* x = a.qkv + (long long)r * a.ld;
-  const int units = a.heads + a.kv_heads;
+  const int kvh = a.kv_shared ? 0 : a.kv_heads;      // key / value heads this row brings (none: they are another layer's)
+  const int units = a.heads + kvh;
   // biases of the projections: added in place before anything reads the row
   if (a.q_bias != nullptr || a.k_bias != nullptr || a.v_bias != nullptr) {
     if (a.q_bias != nullptr)
       for (int i = tid; i < a.heads * a.dim; i += blockDim.x) x[a.q_off + i] += a.q_bias[i];
-    if (a.k_bias != nullptr)
+    if (a.k_bias != nullptr && kvh)
       for (int i = tid; i < a.kv_heads * a.dim; i += blockDim.x) x[a.k_off + i] += a.k_bias[i];
-    if (a.v_bias != nullptr)
+    if (a.v_bias != nullptr && kvh)
       for (int i = tid; i < a.kv_heads * a.vdim; i += blockDim.x) x[a.v_off + i] += a.v_bias[i];
     __syncthreads();
   }
   float* s_vss = s_ss + units + 2;      // [kv_heads] sums of squares of the value heads
-  if (a.v_norm) {
+  if (a.v_norm && kvh) {
     for (int u = warp; u < a.kv_heads; u += n_warps) {
       const float* src = x + a.v_off + u * a.vdim;
       float ss = 0.f;
@@ -185,7 +188,7 @@ window_attn_prep_kernel(WinArgs a, int R, const int* __restrict__ row_seq, const
   const int vhalf = a.v_inv_freq != nullptr ? a.v_rot_dims >> 1 : 0;
   const int vrot = 2 * vhalf;
   const int vper = a.vdim - vhalf;
-  for (int it = tid; it < a.kv_heads * vper; it += blockDim.x) {
+  for (int it = tid; it < kvh * vper; it += blockDim.x) {
     const int g = it / vper, e = it % vper;
     const float* src = x + a.v_off + g * a.vdim;
     float* dst = crow + a.kv_heads * a.dim + g * a.vdim;
@@ -1055,6 +1058,9 @@ static int fill_win(WinArgs& a, const lp_window_attn_desc* d, bool need_q) {
   a.cache = d->cache; a.page_size = d->page_size; a.page_table = d->page_table; a.max_pages = d->max_pages;
   a.pooled = d->pooled; a.pooled_table = d->pooled_table; a.max_pooled_pages = d->max_pooled_pages; a.pool = d->pool;
   a.window = d->window; a.keep_first = d->keep_first;
+  a.chunk = d->chunk; a.kv_shared = d->kv_shared;
+  LP_REQUIRE(d->chunk >= 0, "lp_window_attn: chunk < 0");
+  LP_REQUIRE(d->chunk == 0 || (d->keep_first == 0 && d->pool == 0), "lp_window_attn: block-local visibility with kept tokens or pooled blocks is not supported");
   a.scale = d->scale; a.softcap = d->softcap; a.sink = d->sink;
   a.q_bias = d->q_bias; a.k_bias = d->k_bias; a.v_bias = d->v_bias; a.v_norm = d->v_norm;
   a.talk = d->talk; a.g_off = d->g_off;

@@ -55,6 +55,11 @@ def _gavatar(path, **kw):
     return gavatar.load(path, **kw)
 
 
+def _kamosun(path, **kw):
+    from . import kamosun
+    return kamosun.load(path, **kw)
+
+
 def _llava(path, **kw):
     from .hf import myLlavaForConditionalGeneration
     return myLlavaForConditionalGeneration.from_pretrained(path, **kw)
@@ -63,6 +68,7 @@ def _llava(path, **kw):
 register("Zudalorn", _zudalorn)
 register("Ronelorn", _ronelorn)
 register("Gavatar", _gavatar)
+register("Kamosun", _kamosun)
 register("LlavaForConditionalGeneration", _llava)
 register("myLlavaForConditionalGeneration", _llava)
 register("llava", _llava)

@@ -1,7 +1,8 @@
 """Decoder-only language models described as a LIST OF LAYERS, on the 32-bit residual-stream kernels.
 
 A model is a `SeqLMConfig`: vocabulary, width, norm epsilon and style, and a tuple of `LayerConfig`s, each naming its sequence mixer
-(`RetentionConfig`, `LatentAttentionConfig`, `WindowAttentionConfig`, `MinGRUConfig` or `MLSTMConfig`) and its feed-forward
+(`RetentionConfig`, `LatentAttentionConfig`, `WindowAttentionConfig`, `MinGRUConfig`, `MLSTMConfig`, or a `ParallelMixerConfig` of
+two of them side by side) and its feed-forward
 (`DenseFFConfig`, `MoEConfig` or none); a layer may run on another layer's weights with a cache or state of its own (a looped stack
 is such a list), shift its mixer's input towards the previous token's, and add a learned vector to the stream before it runs.  Every mechanism is a
 separate native entry point with its constants as arguments (include/leopard_b200.h, "32-BIT RESIDUAL-STREAM MODELS"), so another
@@ -54,11 +55,22 @@ class LinearScaling:
 
 
 @dataclass(frozen=True)
+class BandScaling:
+    """Frequency rescale by wavelength bands: a pair whose wavelength is shorter than original / high keeps its frequency f, one
+    whose wavelength is longer than original / low gets f / factor, and between the two the blend (1 - s) f / factor + s f with
+    s = (original / wavelength - low) / (high - low)."""
+    factor: float
+    original: float
+    low: float
+    high: float
+
+
+@dataclass(frozen=True)
 class RotaryConfig:
     dims: int                      # leading dimensions of a head that are rotated
     base: float
     layout: str = "half"           # "half": i pairs with i + dims/2; "interleaved": 2i pairs with 2i + 1
-    scaling: Union[YarnScaling, LinearScaling, None] = None
+    scaling: Union[YarnScaling, LinearScaling, BandScaling, None] = None
 
 
 def rotary_table(rot: RotaryConfig) -> Tuple[torch.Tensor, float]:
@@ -72,6 +84,11 @@ def rotary_table(rot: RotaryConfig) -> Tuple[torch.Tensor, float]:
     s = rot.scaling
     if isinstance(s, LinearScaling):
         f = f / s.factor
+    elif isinstance(s, BandScaling):
+        wavelength = 2 * math.pi / f
+        blend = (s.original / wavelength - s.low) / (s.high - s.low) if s.high != s.low else np.ones_like(f)
+        mixed = (1.0 - blend) * f / s.factor + blend * f
+        f = np.where(wavelength < s.original / s.high, f, np.where(wavelength > s.original / s.low, f / s.factor, mixed))
     elif s is not None:
         def pair_index(turns):      # the (fractional) pair index whose wavelength fits `turns` times into the original context
             return rot.dims * math.log(s.original / (2 * math.pi * turns)) / (2 * math.log(rot.base))
@@ -90,10 +107,14 @@ class RetentionConfig:
     vdim: int
     decay: Tuple[float, ...]
     rot: RotaryConfig
+    # "retention": rotated q and k, k scaled by dim^-1/2, every head's output divided by its root mean square and gated by silu(mix.g h);
+    # "lightning": q, k and v are silu(projection), no rotation and no scale, the concatenated heads are RMS-normed together with the
+    # gain mix.norm and gated by sigmoid(mix.g h)
+    form: str = "retention"
 
     @property
     def k_scale(self) -> float:
-        return self.dim ** -0.5
+        return self.dim ** -0.5 if self.form == "retention" else 1.0
 
 
 @dataclass(frozen=True)
@@ -132,6 +153,11 @@ class WindowAttentionConfig:
     value_norm: bool = False       # every value head is divided by its root mean square before it is cached
     talking_heads: bool = False    # softmax weights mixed over the heads by mix.talk [heads, heads] before they meet the values
     out_gate: bool = False         # the concatenated heads are multiplied by sigmoid(mix.g h)
+    chunk: Optional[int] = None    # position i sees only j <= i of its own block, floor(j / chunk) = floor(i / chunk), counted from position 0
+    out_bias: bool = False         # the output projection has a bias (mix.o.b)
+    # the layer has no key / value tensors: it reads the cache rows of that layer (keys after norm and rotation, values), written
+    # earlier in the same step, with its own queries, visibility and everything else
+    kv_from: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -151,9 +177,23 @@ class MLSTMConfig:
 
 
 @dataclass(frozen=True)
+class ParallelMixerConfig:
+    """Two mixers side by side on the same input (tensors under mix.left.* and mix.right.*); the result is half the sum of the two
+    outputs, each first RMS-normed over the model width with its own plain gain (mix.left.out, mix.right.out)."""
+    left: Union[RetentionConfig, LatentAttentionConfig, WindowAttentionConfig, MinGRUConfig, MLSTMConfig]
+    right: Union[RetentionConfig, LatentAttentionConfig, WindowAttentionConfig, MinGRUConfig, MLSTMConfig]
+
+
+GLU_SLOPE = 1.702                  # the sigmoid's slope in the clamped gated unit
+
+
+@dataclass(frozen=True)
 class DenseFFConfig:
     ff: int
-    act: str = "xielu"             # "xielu" (two learned constants in mlp.act) or "relu2" (the square of relu)
+    # "xielu" (two learned constants in mlp.act), "relu2" (the square of relu), or "clamp_glu": with g = min(mlp.gate h, limit) and
+    # u = clamp(mlp.up h, -limit, limit) the hidden vector is g sigmoid(1.702 g) (u + 1)
+    act: str = "xielu"
+    limit: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -165,13 +205,18 @@ class MoEConfig:
     keep_groups: int = 1
     shared_ff: int = 0             # 0: no shared expert
     # "grouped_sigmoid": sigmoid scores, choice bias, best groups, weights = chosen scores / their sum;
-    # "softmax_top": logits + mlp.router.b, the largest are chosen, weights = softmax over the chosen logits
+    # "softmax_top": logits + mlp.router.b, the largest are chosen, weights = softmax over the chosen logits;
+    # "sigmoid_input": sigmoid scores, the largest are chosen, and a chosen expert runs on score * h (its output is not weighted)
     router: str = "grouped_sigmoid"
+    act: str = "silu_glu"          # the experts' unit: "silu_glu" (silu(gate) * up) or "clamp_glu" (DenseFFConfig) with the limits below
+    limit: float = 0.0
+    shared_limit: float = 0.0
+    shared_gate: bool = True       # the shared expert's output is multiplied by sigmoid(mlp.shared.sg h); False: added as it is
 
 
 @dataclass(frozen=True)
 class LayerConfig:
-    mixer: Union[RetentionConfig, LatentAttentionConfig, WindowAttentionConfig, MinGRUConfig, MLSTMConfig]
+    mixer: Union[RetentionConfig, LatentAttentionConfig, WindowAttentionConfig, MinGRUConfig, MLSTMConfig, ParallelMixerConfig]
     ff: Union[DenseFFConfig, MoEConfig, None]
     weights_of: Optional[int] = None   # run on that layer's tensors (mixer, feed-forward, norms); cache and state stay this layer's own
     # the mixer reads h_t + (h_(t-1) - h_t) * shift per channel instead of h_t (h: the normed stream; the previous token's h is part of
@@ -188,12 +233,20 @@ class SeqLMConfig:
     eps: float
     layers: Tuple[LayerConfig, ...]
     # "sandwich": x <- x + norm_b(sublayer(norm_a(x))), every norm with ONE gain; "pre": x <- x + residual_mult * sublayer(norm(x)),
-    # the norm's gain a vector stored around zero (x / rms * (1 + w)); "sandwich_vector": the sandwich form with such vector gains
+    # the norm's gain a vector stored around zero (x / rms * (1 + w)); "sandwich_vector": the sandwich form with such vector gains;
+    # "parallel_dyt": x <- x + residual_mult * (mixer(norm1(x)) + ff(norm2(x))), both sublayers on the same x, every norm (the final
+    # one too) a Dynamic Tanh tanh(alpha x) * w + b with the tensors <name>, <name>.alpha, <name>.b
     norm: str = "sandwich"
     residual_mult: float = 1.0
     embed_scale: float = 1.0
     # > 0: absolute sinusoidal positions are added to the embedding, entries (2i, 2i + 1) = (sin, cos)(p * base^(-2i / width))
     position_base: float = 0.0
+    # every sublayer's output is multiplied element by element by sigmoid(W h + b) of the sublayer's own input h (rg1, rg1.b for the
+    # mixer, rg2, rg2.b for the feed-forward) before it joins the stream
+    residual_gate: bool = False
+    # what goes on to the next layer (and to the output) is sum_j dwa[j] X_j over the embedding output X_0 and the results X_1 ..
+    # X_(i+1) of the layers so far (the layer's tensor dwa [i + 2])
+    depth_average: bool = False
 
 
 def softplus(x: float) -> float:
@@ -227,14 +280,19 @@ class SeqLMWeights:
         def one_plus(layer, key):           # a gain stored around zero
             return (1.0 + w(layer, key, (cfg.width,)).float()).contiguous().to(dev)
 
-        if cfg.norm not in ("sandwich", "pre", "sandwich_vector"):
+        if cfg.norm not in ("sandwich", "pre", "sandwich_vector", "parallel_dyt"):
             raise ValueError(f"unknown norm style {cfg.norm!r}")
         pre = cfg.norm == "pre"
+        dyt = cfg.norm == "parallel_dyt"
         vector = cfg.norm != "sandwich"
+
+        def dyt_norm(layer, key):           # (alpha, gain, shift) of a Dynamic Tanh
+            return (num(layer, key + ".alpha"), vec(w(layer, key, (cfg.width,))), vec(w(layer, key + ".b", (cfg.width,))))
+
         D = cfg.width
         self.embed = mat(w(None, "embed", (cfg.vocab, D)))
         self.head = mat(w(None, "head", (cfg.vocab, D)))
-        self.final_gain = one_plus(None, "final.norm") if vector else num(None, "final.norm")
+        self.final_gain = dyt_norm(None, "final.norm") if dyt else one_plus(None, "final.norm") if vector else num(None, "final.norm")
         if cfg.position_base > 0:      # frequencies in float64, split into two floats hi + lo
             f64 = cfg.position_base ** (-2.0 * np.arange((D + 1) // 2, dtype=np.float64) / D)
             hi = f64.astype(np.float32)
@@ -261,85 +319,119 @@ class SeqLMWeights:
                     raise ValueError(f"layer {i} differs from layer {j}, whose weights it uses")
                 self.layers.append(None)              # linked below, once every owner is loaded
                 continue
-            if pre:
-                lw: Dict[str, object] = {"norm1": one_plus(i, "norm1")}
+            if dyt:
+                lw: Dict[str, object] = {"norm1": dyt_norm(i, "norm1")}
+            elif pre:
+                lw = {"norm1": one_plus(i, "norm1")}
             elif vector:
                 lw = {k: one_plus(i, k) for k in ("norm1", "norm1b")}
             else:
                 lw = {k: num(i, k) for k in ("norm1", "norm1b")}
             if lc.token_shift:
                 lw["shift"] = vec(w(i, "shift", (D,)))
+            def mixer_weights(m, pfx: str) -> Dict[str, object]:
+                """the tensors of one mixer, named <pfx><key> in the checkpoint"""
+                mw: Dict[str, object] = {}
+                if not isinstance(m, (MinGRUConfig, MLSTMConfig)):
+                    inv_freq, mag = rotary_table(m.rot)
+                    mw["inv_freq"], mw["rot_mag"] = inv_freq.to(dev), mag
+                if isinstance(m, MLSTMConfig):
+                    hd, hv = m.heads * m.dim, m.heads * m.vdim
+                    mw["w_proj"] = mat(torch.cat([w(i, pfx + "q", (hd, D)), w(i, pfx + "k", (hd, D)), w(i, pfx + "v", (hv, D)), w(i, pfx + "g", (hv, D)),
+                                                  w(i, pfx + "i", (m.heads, D)), w(i, pfx + "f", (m.heads, D))], 0))
+                    mw["i_bias"], mw["f_bias"] = vec(w(i, pfx + "i.b", (m.heads,))), vec(w(i, pfx + "f.b", (m.heads,)))
+                    mw["out_gain"] = vec(w(i, pfx + "norm", (hv,)))
+                    mw["w_o"] = mat(w(i, pfx + "o", (D, hv)))
+                elif isinstance(m, MinGRUConfig):
+                    mw["w_zxg"] = mat(torch.cat([w(i, pfx + "z", (m.width, D)), w(i, pfx + "x", (m.width, D)), w(i, pfx + "g", (m.width, D))], 0))
+                    mw["z_bias"], mw["x_bias"] = vec(w(i, pfx + "z.b", (m.width,))), vec(w(i, pfx + "x.b", (m.width,)))
+                    mw["w_o"] = mat(w(i, pfx + "o", (D, m.width)))
+                elif isinstance(m, WindowAttentionConfig):
+                    if m.heads % m.kv_heads:
+                        raise ValueError(f"layer {i}: {m.heads} query heads over {m.kv_heads} key / value heads")
+                    parts = [w(i, pfx + "q", (m.heads * m.dim, D))]
+                    if m.kv_from is None:
+                        parts += [w(i, pfx + "k", (m.kv_heads * m.dim, D)), w(i, pfx + "v", (m.kv_heads * m.vdim, D))]
+                    if m.out_gate:
+                        parts.append(w(i, pfx + "g", (m.heads * m.vdim, D)))
+                    mw["w_qkv"] = mat(torch.cat(parts, 0))
+                    if m.bias:
+                        mw["q_bias"] = vec(w(i, pfx + "q.b", (m.heads * m.dim,)))
+                        if m.kv_from is None:
+                            mw["k_bias"], mw["v_bias"] = vec(w(i, pfx + "k.b", (m.kv_heads * m.dim,))), vec(w(i, pfx + "v.b", (m.kv_heads * m.vdim,)))
+                    if m.out_bias:
+                        mw["o_bias"] = vec(w(i, pfx + "o.b", (D,)))
+                    if m.talking_heads:
+                        mw["talk"] = vec(w(i, pfx + "talk", (m.heads, m.heads)))
+                    elif m.out_gate:      # the gate rides on the mixing kernel: no mixing is the unit matrix
+                        mw["talk"] = torch.eye(m.heads, dtype=F32).to(dev)
+                    if (m.talking_heads or m.out_gate) and m.value_rot is not None:
+                        raise ValueError(f"layer {i}: mixed or gated heads with rotated values are not supported")
+                    if m.qk_norm == "head":      # a layer without keys of its own hands the kernel its query gain twice (the second is unused)
+                        mw["q_gain"] = vec(w(i, pfx + "q.norm", (m.dim,)))
+                        mw["k_gain"] = vec(w(i, pfx + "k.norm", (m.dim,))) if m.kv_from is None else mw["q_gain"]
+                    elif m.qk_norm == "full":
+                        mw["q_gain"] = vec(w(i, pfx + "q.norm", (m.heads * m.dim,)))
+                        mw["k_gain"] = vec(w(i, pfx + "k.norm", (m.kv_heads * m.dim,))) if m.kv_from is None else mw["q_gain"]
+                    elif m.qk_norm not in ("none", "unit"):
+                        raise ValueError(f"layer {i}: unknown query / key norm {m.qk_norm!r}")
+                    if m.value_rot is not None:
+                        mw["v_inv_freq"] = rotary_table(m.value_rot)[0].to(dev)
+                    mw["w_o"] = mat(w(i, pfx + "o", (D, m.heads * m.vdim)))
+                elif isinstance(m, RetentionConfig):
+                    if len(m.decay) != m.heads:
+                        raise ValueError(f"layer {i}: {len(m.decay)} decays for {m.heads} heads")
+                    mw["w_qkvg"] = mat(torch.cat([w(i, pfx + "q", (m.heads * m.dim, D)), w(i, pfx + "k", (m.heads * m.dim, D)),
+                                                  w(i, pfx + "v", (m.heads * m.vdim, D)), w(i, pfx + "g", (m.heads * m.vdim, D))], 0))
+                    mw["w_o"] = mat(w(i, pfx + "o", (D, m.heads * m.vdim)))
+                    mw["decay"] = torch.tensor(m.decay, dtype=torch.float64).to(F32).to(dev)
+                    if m.form == "lightning":
+                        mw["out_gain"] = vec(w(i, pfx + "norm", (m.heads * m.vdim,)))
+                    elif m.form != "retention":
+                        raise ValueError(f"layer {i}: unknown retention form {m.form!r}")
+                else:
+                    per = m.dim + m.rot_dim
+                    # one product of h: [queries or their latent | key / value latent (+ shared rotated key) | one gate per head]
+                    parts = [w(i, pfx + "dq", (m.q_rank, D)) if m.q_rank else w(i, pfx + "q", (m.heads * per, D)),
+                             w(i, pfx + "dkv", (m.kv_rank + m.rot_dim, D))]
+                    if m.head_gate:
+                        parts.append(w(i, pfx + "g", (m.heads, D)))
+                    mw["w_qdkv"] = mat(torch.cat(parts, 0))
+                    if m.q_rank:
+                        mw["cq_gain"] = vec(w(i, pfx + "dq.norm", (m.q_rank,)))
+                        mw["w_uq"] = mat(w(i, pfx + "uq", (m.heads * per, m.q_rank)))
+                    if m.sink:
+                        mw["sink"] = vec(w(i, pfx + "sink", (m.heads,)))
+                    mw["c_gain"] = w(i, pfx + "dkv.norm", (m.kv_rank,)).float().contiguous().to(dev)
+                    uk = w(i, pfx + "uk", (m.heads * m.dim, m.kv_rank))
+                    mw["w_ukT"] = mat(uk.reshape(m.heads, m.dim, m.kv_rank).transpose(1, 2))       # [heads][kv_rank, dim]
+                    mw["w_uv"] = mat(w(i, pfx + "uv", (m.heads * m.vdim, m.kv_rank)))                 # [heads][vdim, kv_rank]
+                    mw["w_o"] = mat(w(i, pfx + "o", (D, m.heads * m.vdim)))
+                return mw
+
             m = lc.mixer
-            if not isinstance(m, (MinGRUConfig, MLSTMConfig)):
-                inv_freq, mag = rotary_table(m.rot)
-                lw["inv_freq"], lw["rot_mag"] = inv_freq.to(dev), mag
-            if isinstance(m, MLSTMConfig):
-                hd, hv = m.heads * m.dim, m.heads * m.vdim
-                lw["w_proj"] = mat(torch.cat([w(i, "mix.q", (hd, D)), w(i, "mix.k", (hd, D)), w(i, "mix.v", (hv, D)), w(i, "mix.g", (hv, D)),
-                                              w(i, "mix.i", (m.heads, D)), w(i, "mix.f", (m.heads, D))], 0))
-                lw["i_bias"], lw["f_bias"] = vec(w(i, "mix.i.b", (m.heads,))), vec(w(i, "mix.f.b", (m.heads,)))
-                lw["out_gain"] = vec(w(i, "mix.norm", (hv,)))
-                lw["w_o"] = mat(w(i, "mix.o", (D, hv)))
-            elif isinstance(m, MinGRUConfig):
-                lw["w_zxg"] = mat(torch.cat([w(i, "mix.z", (m.width, D)), w(i, "mix.x", (m.width, D)), w(i, "mix.g", (m.width, D))], 0))
-                lw["z_bias"], lw["x_bias"] = vec(w(i, "mix.z.b", (m.width,))), vec(w(i, "mix.x.b", (m.width,)))
-                lw["w_o"] = mat(w(i, "mix.o", (D, m.width)))
-            elif isinstance(m, WindowAttentionConfig):
-                if m.heads % m.kv_heads:
-                    raise ValueError(f"layer {i}: {m.heads} query heads over {m.kv_heads} key / value heads")
-                parts = [w(i, "mix.q", (m.heads * m.dim, D)), w(i, "mix.k", (m.kv_heads * m.dim, D)), w(i, "mix.v", (m.kv_heads * m.vdim, D))]
-                if m.out_gate:
-                    parts.append(w(i, "mix.g", (m.heads * m.vdim, D)))
-                lw["w_qkv"] = mat(torch.cat(parts, 0))
-                if m.bias:
-                    lw["q_bias"], lw["k_bias"] = vec(w(i, "mix.q.b", (m.heads * m.dim,))), vec(w(i, "mix.k.b", (m.kv_heads * m.dim,)))
-                    lw["v_bias"] = vec(w(i, "mix.v.b", (m.kv_heads * m.vdim,)))
-                if m.talking_heads:
-                    lw["talk"] = vec(w(i, "mix.talk", (m.heads, m.heads)))
-                elif m.out_gate:      # the gate rides on the mixing kernel: no mixing is the unit matrix
-                    lw["talk"] = torch.eye(m.heads, dtype=F32).to(dev)
-                if (m.talking_heads or m.out_gate) and m.value_rot is not None:
-                    raise ValueError(f"layer {i}: mixed or gated heads with rotated values are not supported")
-                if m.qk_norm == "head":
-                    lw["q_gain"], lw["k_gain"] = vec(w(i, "mix.q.norm", (m.dim,))), vec(w(i, "mix.k.norm", (m.dim,)))
-                elif m.qk_norm == "full":
-                    lw["q_gain"] = vec(w(i, "mix.q.norm", (m.heads * m.dim,)))
-                    lw["k_gain"] = vec(w(i, "mix.k.norm", (m.kv_heads * m.dim,)))
-                elif m.qk_norm not in ("none", "unit"):
-                    raise ValueError(f"layer {i}: unknown query / key norm {m.qk_norm!r}")
-                if m.value_rot is not None:
-                    lw["v_inv_freq"] = rotary_table(m.value_rot)[0].to(dev)
-                lw["w_o"] = mat(w(i, "mix.o", (D, m.heads * m.vdim)))
-            elif isinstance(m, RetentionConfig):
-                if len(m.decay) != m.heads:
-                    raise ValueError(f"layer {i}: {len(m.decay)} decays for {m.heads} heads")
-                lw["w_qkvg"] = mat(torch.cat([w(i, "mix.q", (m.heads * m.dim, D)), w(i, "mix.k", (m.heads * m.dim, D)),
-                                              w(i, "mix.v", (m.heads * m.vdim, D)), w(i, "mix.g", (m.heads * m.vdim, D))], 0))
-                lw["w_o"] = mat(w(i, "mix.o", (D, m.heads * m.vdim)))
-                lw["decay"] = torch.tensor(m.decay, dtype=torch.float64).to(F32).to(dev)
+            if isinstance(m, ParallelMixerConfig):
+                for side, sub in (("left", m.left), ("right", m.right)):
+                    if isinstance(sub, ParallelMixerConfig) or getattr(sub, "kv_from", None) is not None:
+                        raise ValueError(f"layer {i}: a branch of a parallel mixer is a plain mixer with a cache of its own")
+                    lw[side] = mixer_weights(sub, f"mix.{side}.")
+                    lw[side + "_out"] = (0.5 * w(i, f"mix.{side}.out", (D,)).float()).contiguous().to(dev)      # the halving rides on the gain
             else:
-                per = m.dim + m.rot_dim
-                # one product of h: [queries or their latent | key / value latent (+ shared rotated key) | one gate per head]
-                parts = [w(i, "mix.dq", (m.q_rank, D)) if m.q_rank else w(i, "mix.q", (m.heads * per, D)),
-                         w(i, "mix.dkv", (m.kv_rank + m.rot_dim, D))]
-                if m.head_gate:
-                    parts.append(w(i, "mix.g", (m.heads, D)))
-                lw["w_qdkv"] = mat(torch.cat(parts, 0))
-                if m.q_rank:
-                    lw["cq_gain"] = vec(w(i, "mix.dq.norm", (m.q_rank,)))
-                    lw["w_uq"] = mat(w(i, "mix.uq", (m.heads * per, m.q_rank)))
-                if m.sink:
-                    lw["sink"] = vec(w(i, "mix.sink", (m.heads,)))
-                lw["c_gain"] = w(i, "mix.dkv.norm", (m.kv_rank,)).float().contiguous().to(dev)
-                uk = w(i, "mix.uk", (m.heads * m.dim, m.kv_rank))
-                lw["w_ukT"] = mat(uk.reshape(m.heads, m.dim, m.kv_rank).transpose(1, 2))       # [heads][kv_rank, dim]
-                lw["w_uv"] = mat(w(i, "mix.uv", (m.heads * m.vdim, m.kv_rank)))                 # [heads][vdim, kv_rank]
-                lw["w_o"] = mat(w(i, "mix.o", (D, m.heads * m.vdim)))
+                lw.update(mixer_weights(m, "mix."))
+            if cfg.residual_gate:
+                lw["w_rg1"], lw["rg1_bias"] = mat(w(i, "rg1", (D, D))), vec(w(i, "rg1.b", (D,)))
+                if lc.ff is not None:
+                    lw["w_rg2"], lw["rg2_bias"] = mat(w(i, "rg2", (D, D))), vec(w(i, "rg2.b", (D,)))
+            if cfg.depth_average:
+                lw["dwa"] = vec(w(i, "dwa", (i + 2,)))
             f = lc.ff
             if f is not None:
-                lw.update({"norm2": one_plus(i, "norm2")} if pre else
+                lw.update({"norm2": dyt_norm(i, "norm2")} if dyt else {"norm2": one_plus(i, "norm2")} if pre else
                           {k: (one_plus(i, k) if vector else num(i, k)) for k in ("norm2", "norm2b")})
-            if isinstance(f, DenseFFConfig):
+            if isinstance(f, DenseFFConfig) and f.act == "clamp_glu":
+                lw["w_gu"] = mat(torch.cat([w(i, "mlp.gate", (f.ff, D)), w(i, "mlp.up", (f.ff, D))], 0))
+                lw["w_down"] = mat(w(i, "mlp.down", (D, f.ff)))
+            elif isinstance(f, DenseFFConfig):
                 lw["w_up"] = mat(w(i, "mlp.up", (f.ff, D)))
                 lw["w_down"] = mat(w(i, "mlp.down", (D, f.ff)))
                 if f.act == "xielu":
@@ -349,10 +441,15 @@ class SeqLMWeights:
                     raise ValueError(f"layer {i}: unknown activation {f.act!r}")
             elif isinstance(f, MoEConfig):
                 lw["w_router"] = mat(w(i, "mlp.router", (f.experts, D)))
+                if f.act not in ("silu_glu", "clamp_glu"):
+                    raise ValueError(f"layer {i}: unknown expert unit {f.act!r}")
                 if f.router == "softmax_top":
                     if f.shared_ff or f.n_groups != 1:
                         raise ValueError(f"layer {i}: the softmax router has neither groups nor a shared expert")
                     lw["router_bias"] = vec(w(i, "mlp.router.b", (f.experts,)))
+                elif f.router == "sigmoid_input":
+                    if f.n_groups != 1:
+                        raise ValueError(f"layer {i}: the plain sigmoid router has no groups")
                 elif f.router != "grouped_sigmoid":
                     raise ValueError(f"layer {i}: unknown router {f.router!r}")
                 else:
@@ -368,7 +465,8 @@ class SeqLMWeights:
                 if f.shared_ff:
                     lw["ws_gu"] = mat(torch.cat([w(i, "mlp.shared.gate", (f.shared_ff, D)), w(i, "mlp.shared.up", (f.shared_ff, D))], 0))
                     lw["ws_down"] = mat(w(i, "mlp.shared.down", (D, f.shared_ff)))
-                    lw["w_sg"] = mat(w(i, "mlp.shared.sg").reshape(D))
+                    if f.shared_gate:
+                        lw["w_sg"] = mat(w(i, "mlp.shared.sg").reshape(D))
             self.layers.append(lw)
         for i, lc in enumerate(cfg.layers):
             if lc.weights_of is not None:
@@ -484,19 +582,32 @@ class SeqLMEngine:
         self.L = lib
         self.dtype = dtype
         self.act = BF16 if dtype == "bfloat16" else F32
-        # what every layer keeps per request: rows of a paged cache (attention), rows of a summary pool (pooled blocks), a state
+        # what every mixer keeps per request: rows of a paged cache (attention), rows of a summary pool (pooled blocks), a state.
+        # The tables are keyed by the layer, or by (layer, "left" | "right") for the branches of a parallel mixer.
         rows, states, summaries, looks, keep = [], [], [], [], 0
-        self._cache_index, self._state_index, self._summary_index, self._shift_index = [], [], [], []
-        for lc in cfg.layers:
-            m = lc.mixer
+        self._cache_index, self._state_index, self._summary_index, self._shift_index = {}, {}, {}, []
+
+        def look_back(m):      # how far back a windowed or block-local layer reads (None: everything)
+            bounds = [v for v in (m.window, m.chunk) if v and v > 0]
+            return min(bounds) if bounds else None
+
+        def claim(key, m):
+            nonlocal keep
             ci = si = pi = -1
-            self._shift_index.append(len(states) if lc.token_shift else -1)
-            if lc.token_shift:
-                states.append((cfg.width,))
             if isinstance(m, LatentAttentionConfig):
                 ci = len(rows)
                 rows.append(m.kv_rank + m.rot_dim)
                 looks.append(m.window if m.window and m.window > 0 else None)
+            elif isinstance(m, WindowAttentionConfig) and m.kv_from is not None:
+                j = m.kv_from
+                src = cfg.layers[j].mixer if 0 <= j < len(cfg.layers) and not isinstance(key, tuple) and j < key else None
+                if not isinstance(src, WindowAttentionConfig) or src.kv_from is not None:
+                    raise ValueError(f"layer {key}: kv_from = {j} must name an earlier attention layer that has keys and values of its own")
+                if (src.kv_heads, src.dim, src.vdim, src.rot) != (m.kv_heads, m.dim, m.vdim, m.rot) or m.pool or src.value_rot or m.value_rot:
+                    raise ValueError(f"layer {key}: its key / value sizes and rotation differ from those of layer {j}, whose cache it reads")
+                ci = self._cache_index[j]
+                looks.append(look_back(m))      # the owner's rows must stay for as long as this layer looks back
+                keep = max(keep, m.keep_first if look_back(m) else 0)
             elif isinstance(m, WindowAttentionConfig):
                 ci = len(rows)
                 rows.append(m.kv_heads * (m.dim + m.vdim))
@@ -505,7 +616,7 @@ class SeqLMEngine:
                     pi = len(summaries)
                     summaries.append((m.kv_heads * (m.dim + m.vdim), m.pool))
                 # a pooled layer reads a block's tokens once more when the block is complete
-                looks.append(max(m.window, m.pool) if windowed else None)
+                looks.append(max(m.window, m.pool) if windowed and m.pool > 0 else look_back(m))
                 keep = max(keep, m.keep_first if windowed else 0)
             elif isinstance(m, RetentionConfig):
                 si = len(states)
@@ -518,9 +629,17 @@ class SeqLMEngine:
                 states.append((m.heads, m.dim + 1, m.vdim + 1))      # per head S | n, and the running maximum in the last row
             else:
                 raise TypeError(f"unknown mixer {type(m).__name__}")
-            self._cache_index.append(ci)
-            self._state_index.append(si)
-            self._summary_index.append(pi)
+            self._cache_index[key], self._state_index[key], self._summary_index[key] = ci, si, pi
+
+        for li, lc in enumerate(cfg.layers):
+            self._shift_index.append(len(states) if lc.token_shift else -1)
+            if lc.token_shift:
+                states.append((cfg.width,))
+            if isinstance(lc.mixer, ParallelMixerConfig):
+                claim((li, "left"), lc.mixer.left)
+                claim((li, "right"), lc.mixer.right)
+            else:
+                claim(li, lc.mixer)
         window = None if any(x is None for x in looks) else max(looks, default=None)
         self.cache = SequenceCache(rows, states, window, self.device, max_tokens=max_tokens, page_size=page_size, max_seqs=max_seqs,
                                    keep_first=keep, summaries=summaries)
@@ -552,38 +671,48 @@ class SeqLMEngine:
                 and N % 8 == 0 and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.stride(1) == 1
                 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
-    def linear(self, a: torch.Tensor, w: torch.Tensor, out_dtype, epi=_lib.EPI_NONE, epi_a=0.0, epi_b=0.0, out=None, into=None):
-        """out[M, N'] = epi(a[M, K] @ w[N, K].T); with into = (x fp32 [M, N'], m): x <- x + m * epi(...) and x is returned."""
+    def linear(self, a: torch.Tensor, w: torch.Tensor, out_dtype, epi=_lib.EPI_NONE, epi_a=0.0, epi_b=0.0, out=None, into=None, bias=None,
+               row_scale=None):
+        """out[M, N'] = epi(row_scale[m] * (a[M, K] @ w[N, K].T) + bias[N]) (bias, row_scale: fp32 device vectors or None).  With
+        into = (x fp32 [M, N'], m) or (x, m, gate fp32 [M, N']): x <- x + m * epi(...) (* sigmoid(gate)) and x is returned."""
         M, K = a.shape
         N = w.shape[0]
-        n_out = N // 2 if epi == _lib.EPI_SILU_GATE else N
+        n_out = N // 2 if epi in _lib.GATED_EPIS else N
+        # a row scale reaches the tensor-core path only through the activation kernel that follows the product
+        tc = self._on_tensor_cores(a, w, M, N, K) and (row_scale is None or (epi != _lib.EPI_NONE and bias is None))
         if into is not None:
-            x, mult = into
-            if self._on_tensor_cores(a, w, M, N, K):
-                y = self.linear(a, w, F32, epi, epi_a, epi_b)
-                rc = self.L.lp_axpy_f32(_lib.ptr(x), x.stride(0), _lib.ptr(y), y.stride(0), float(mult), M, n_out, self._stream())
+            x, mult = into[0], into[1]
+            gate = into[2] if len(into) > 2 else None
+            if tc:
+                y = self.linear(a, w, F32, epi, epi_a, epi_b, bias=bias, row_scale=row_scale)
+                if gate is None:
+                    rc = self.L.lp_axpy_f32(_lib.ptr(x), x.stride(0), _lib.ptr(y), y.stride(0), float(mult), M, n_out, self._stream())
+                else:
+                    rc = self.L.lp_gated_axpy_f32(_lib.ptr(x), x.stride(0), _lib.ptr(y), y.stride(0), None, _lib.ptr(gate), gate.stride(0), None,
+                                                  float(mult), M, n_out, self._stream())
                 self._check(rc, "lp_axpy_f32")
                 return x
             d = _lib.LinearDesc(A=_lib.ptr(a), lda=a.stride(0), a_batch=0, a_fp32=int(a.dtype == F32), W=_lib.ptr(w), ldw=w.stride(0),
                                 w_batch=0, C=_lib.ptr(x), ldc=x.stride(0), c_batch=0, c_fp32=1, M=M, N=N, K=K, batch=1, epi=epi,
-                                epi_a=epi_a, epi_b=epi_b, c_accum=1, c_scale=float(mult))
+                                epi_a=epi_a, epi_b=epi_b, c_accum=1, c_scale=float(mult), bias=_lib.ptr(bias), row_scale=_lib.ptr(row_scale),
+                                gate=_lib.ptr(gate), ldg=gate.stride(0) if gate is not None else 0)
             self._check(self.L.lp_linear(C.byref(d), self._stream()), "lp_linear")
             return x
         if out is None:
             out = self._empty((M, n_out), out_dtype)
-        if self._on_tensor_cores(a, w, M, N, K) and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
+        if tc and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
             raw = out if epi == _lib.EPI_NONE else self._empty((M, N), F32)
-            rc = self.L.lp_gemm_bf16(_lib.ptr(a), a.stride(0), _lib.ptr(w), w.stride(0), _lib.ptr(raw), raw.stride(0), M, N, K, None, None,
-                                     0, 0, _lib.ACT_NONE, int(raw.dtype == F32), 0, self._stream())
+            rc = self.L.lp_gemm_bf16(_lib.ptr(a), a.stride(0), _lib.ptr(w), w.stride(0), _lib.ptr(raw), raw.stride(0), M, N, K, _lib.ptr(bias),
+                                     None, 0, 0, _lib.ACT_NONE, int(raw.dtype == F32), 0, self._stream())
             self._check(rc, "lp_gemm_bf16")
             if epi != _lib.EPI_NONE:
-                rc = self.L.lp_glu_f32(_lib.ptr(raw), raw.stride(0), 1, _lib.ptr(out), out.stride(0), int(out.dtype == F32), M, n_out, epi,
-                                       epi_a, epi_b, self._stream())
+                rc = self.L.lp_glu_scaled_f32(_lib.ptr(raw), raw.stride(0), 1, _lib.ptr(out), out.stride(0), int(out.dtype == F32), M, n_out,
+                                              epi, epi_a, epi_b, _lib.ptr(row_scale), self._stream())
                 self._check(rc, "lp_glu_f32")
             return out
         d = _lib.LinearDesc(A=_lib.ptr(a), lda=a.stride(0), a_batch=0, a_fp32=int(a.dtype == F32), W=_lib.ptr(w), ldw=w.stride(0),
                             w_batch=0, C=_lib.ptr(out), ldc=out.stride(0), c_batch=0, c_fp32=int(out.dtype == F32), M=M, N=N, K=K,
-                            batch=1, epi=epi, epi_a=epi_a, epi_b=epi_b)
+                            batch=1, epi=epi, epi_a=epi_a, epi_b=epi_b, bias=_lib.ptr(bias), row_scale=_lib.ptr(row_scale))
         self._check(self.L.lp_linear(C.byref(d), self._stream()), "lp_linear")
         return out
 
@@ -608,17 +737,31 @@ class SeqLMEngine:
         self._check(rc, "lp_rmsnorm_f32")
         return out
 
+    def dyt(self, x: torch.Tensor, first, second=None):
+        """Dynamic Tanh of the same rows with one or two parameter sets (alpha, gain, shift): the operands of a layer's sublayers"""
+        M, D = x.shape
+        out = self._empty((M, D), self.act)
+        out2 = self._empty((M, D), self.act) if second is not None else None
+        a2, g2, b2 = second if second is not None else (0.0, None, None)
+        rc = self.L.lp_dyt_f32(_lib.ptr(x), x.stride(0), M, D, first[0], _lib.ptr(first[1]), _lib.ptr(first[2]), _lib.ptr(out), out.stride(0),
+                               a2, _lib.ptr(g2), _lib.ptr(b2), _lib.ptr(out2), out2.stride(0) if out2 is not None else 0,
+                               int(self.act == F32), self._stream())
+        self._check(rc, "lp_dyt_f32")
+        return out, out2
+
     # ------------------------------------------------------------------ mixers
     def _retention(self, li: int, m: RetentionConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
         qkvg = self.linear(h, lw["w_qkvg"], F32)
         hd, hv = m.heads * m.dim, m.heads * m.vdim
-        out = self._empty((b.R, hv), self.act)
+        lightning = m.form == "lightning"      # the raw read-out in fp32; its norm spans the heads and follows below
+        out = self._empty((b.R, hv), F32 if lightning else self.act)
         state = self.cache.states[self._state_index[li]]
         d = _lib.RetentionDesc(qkvg=_lib.ptr(qkvg), ld=qkvg.stride(0), q_off=0, k_off=hd, v_off=2 * hd, g_off=2 * hd + hv, heads=m.heads,
                                dim=m.dim, vdim=m.vdim, decay=_lib.ptr(lw["decay"]), inv_freq=_lib.ptr(lw["inv_freq"]), rot_dims=m.rot.dims,
                                rot_layout=_lib.ROT_INTERLEAVED if m.rot.layout == "interleaved" else _lib.ROT_HALF,
                                rot_mscale=lw["rot_mag"], k_scale=m.k_scale, eps=self.cfg.eps, state=_lib.ptr(state),
-                               slot_stride=state.stride(0), out=_lib.ptr(out), ldo=out.stride(0), out_fp32=int(out.dtype == F32))
+                               slot_stride=state.stride(0), out=_lib.ptr(out), ldo=out.stride(0), out_fp32=int(out.dtype == F32),
+                               in_act=int(lightning), finish=_lib.RET_FINISH_RAW if lightning else _lib.RET_FINISH_GATED_NORM)
         if b.decode:
             rc = self.L.lp_retention_decode(C.byref(d), b.n, _lib.ptr(b.seq_row0), _lib.ptr(b.seq_pos0), _lib.ptr(b.seq_slot), self._stream())
             self._check(rc, "lp_retention_decode")
@@ -629,6 +772,13 @@ class SeqLMEngine:
                                              _lib.ptr(b.seq_chunk0), _lib.ptr(b.chunk_seq), _lib.ptr(b.chunk_row0), _lib.ptr(b.chunk_len),
                                              _lib.ptr(ws), nbytes, self._stream())
             self._check(rc, "lp_retention_prefill")
+        if lightning:
+            gate = qkvg[:, 2 * hd + hv:]
+            normed = self._empty((b.R, hv), self.act)
+            rc = self.L.lp_rmsnorm_gated_f32(_lib.ptr(out), out.stride(0), b.R, hv, _lib.ptr(lw["out_gain"]), self.cfg.eps, _lib.ptr(gate),
+                                             qkvg.stride(0), _lib.ptr(normed), normed.stride(0), int(normed.dtype == F32), self._stream())
+            self._check(rc, "lp_rmsnorm_gated_f32")
+            out = normed
         return self.linear(out, lw["w_o"], F32, into=into)
 
     def _latent(self, li: int, m: LatentAttentionConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
@@ -661,8 +811,8 @@ class SeqLMEngine:
         return self.linear(o, lw["w_o"], F32, into=into)
 
     def _window_attention(self, li: int, m: WindowAttentionConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
-        qkv = self.linear(h, lw["w_qkv"], F32)
-        hq, hk = m.heads * m.dim, m.kv_heads * m.dim
+        qkv = self.linear(h, lw["w_qkv"], F32)      # a layer that reads another layer's keys and values projects its queries only
+        hq, hk = m.heads * m.dim, m.kv_heads * m.dim if m.kv_from is None else 0
         cache = self.cache
         pool = cache.pools[self._cache_index[li]]
         windowed = bool(m.window and m.window > 0)
@@ -676,7 +826,8 @@ class SeqLMEngine:
             vdim=m.vdim,
             norm_mode={"none": _lib.QKNORM_NONE, "head": _lib.QKNORM_HEAD, "unit": _lib.QKNORM_HEAD, "full": _lib.QKNORM_FULL}[m.qk_norm],
             q_bias=_lib.ptr(lw.get("q_bias")), k_bias=_lib.ptr(lw.get("k_bias")), v_bias=_lib.ptr(lw.get("v_bias")),
-            v_norm=int(m.value_norm), talk=_lib.ptr(lw.get("talk")), g_off=hq + hk + m.kv_heads * m.vdim if m.out_gate else -1,
+            v_norm=int(m.value_norm), talk=_lib.ptr(lw.get("talk")),
+            g_off=hq + hk + (m.kv_heads * m.vdim if m.kv_from is None else 0) if m.out_gate else -1,
             q_gain=_lib.ptr(lw.get("q_gain")), k_gain=_lib.ptr(lw.get("k_gain")), eps=self.cfg.eps, inv_freq=_lib.ptr(lw["inv_freq"]),
             rot_dims=m.rot.dims, rot_layout=layouts[m.rot.layout], rot_mscale=lw["rot_mag"],
             v_inv_freq=_lib.ptr(lw.get("v_inv_freq")), v_rot_dims=vr.dims if vr else 0, v_rot_layout=layouts[vr.layout] if vr else 0,
@@ -685,7 +836,7 @@ class SeqLMEngine:
             pooled_table=_lib.ptr(b.summary_table[stream]) if pi >= 0 else None,
             max_pooled_pages=b.summary_width[stream] if pi >= 0 else 0, pool=m.pool if pi >= 0 else 0,
             window=m.window if windowed else 0, keep_first=m.keep_first if windowed else 0, scale=m.scale, softcap=m.softcap,
-            sink=int(m.sink))
+            sink=int(m.sink), chunk=m.chunk or 0, kv_shared=int(m.kv_from is not None))
         st = self._stream()
         self._check(self.L.lp_window_attn_prep(C.byref(d), b.R, _lib.ptr(b.row_seq), _lib.ptr(b.row_pos), st), "lp_window_attn_prep")
         if pi >= 0:
@@ -708,7 +859,7 @@ class SeqLMEngine:
             rc = self.L.lp_window_attn_tiles(C.byref(d), b.R, _lib.ptr(b.row_seq), _lib.ptr(b.row_pos), b.n_chunks, _lib.ptr(b.chunk_seq),
                                              _lib.ptr(b.chunk_row0), _lib.ptr(b.chunk_len), _lib.ptr(o), o.stride(0), int(o.dtype == F32), st)
         self._check(rc, "lp_window_attn")
-        return self.linear(o, lw["w_o"], F32, into=into)
+        return self.linear(o, lw["w_o"], F32, into=into, bias=lw.get("o_bias"))
 
     def _mingru(self, li: int, m: MinGRUConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
         zxg = self.linear(h, lw["w_zxg"], F32)
@@ -746,7 +897,25 @@ class SeqLMEngine:
         self._check(rc, "lp_mlstm")
         return self.linear(out, lw["w_o"], F32, into=into)
 
-    def _mix(self, li: int, m, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
+    def _parallel(self, li: int, m: ParallelMixerConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
+        """two mixers on the same input; each output is RMS-normed over the width with its own gain (which carries the halving)"""
+        left = self._mix((li, "left"), m.left, lw["left"], h, b)
+        right = self._mix((li, "right"), m.right, lw["right"], h, b)
+        mix = self.norm(left, lw["left_out"], F32)
+        self.norm(right, lw["right_out"], accum=mix)
+        if into is None:
+            return mix
+        x, mult = into[0], into[1]
+        gate = into[2] if len(into) > 2 else None
+        rc = self.L.lp_gated_axpy_f32(_lib.ptr(x), x.stride(0), _lib.ptr(mix), mix.stride(0), None, _lib.ptr(gate),
+                                      gate.stride(0) if gate is not None else 0, None, float(mult), b.R, self.cfg.width, self._stream())
+        self._check(rc, "lp_gated_axpy_f32")
+        return x
+
+    def _mix(self, li, m, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
+        """li: the key of the mixer's cache and state — the layer, or (layer, side) for a branch of a parallel mixer"""
+        if isinstance(m, ParallelMixerConfig):
+            return self._parallel(li, m, lw, h, b, into)
         if isinstance(m, MLSTMConfig):
             return self._mlstm(li, m, lw, h, b, into)
         if isinstance(m, RetentionConfig):
@@ -759,7 +928,9 @@ class SeqLMEngine:
 
     # ------------------------------------------------------------------ feed-forwards
     def _dense(self, f: DenseFFConfig, lw, h: torch.Tensor, into=None) -> torch.Tensor:
-        if f.act == "relu2":
+        if f.act == "clamp_glu":
+            up = self.linear(h, lw["w_gu"], self.act, _lib.EPI_CLAMP_GLU, f.limit, GLU_SLOPE)
+        elif f.act == "relu2":
             up = self.linear(h, lw["w_up"], self.act, _lib.EPI_RELU2)
         else:
             up = self.linear(h, lw["w_up"], self.act, _lib.EPI_XIELU, lw["act_a"], lw["act_b"])
@@ -770,15 +941,20 @@ class SeqLMEngine:
         L, st = self.L, self._stream()
         idx = self._empty((T, f.top), I32)
         wts = self._empty((T, f.top), F32)
-        gate = self._empty((T,), F32) if f.shared_ff else None
-        if f.router == "softmax_top":
+        gate = self._empty((T,), F32) if f.shared_ff and f.shared_gate and f.router == "grouped_sigmoid" else None
+        on_input = f.router == "sigmoid_input"      # the weight scales the expert's input: a row scale of its first product
+        epi, epi_a, epi_b = (_lib.EPI_CLAMP_GLU, f.limit, GLU_SLOPE) if f.act == "clamp_glu" else (_lib.EPI_SILU_GATE, 0.0, 0.0)
+        if on_input:
+            rc = L.lp_moe_route_sigmoid(_lib.ptr(h), h.stride(0), int(h.dtype == F32), T, D, _lib.ptr(lw["w_router"]),
+                                        lw["w_router"].stride(0), f.experts, f.top, _lib.ptr(idx), _lib.ptr(wts), st)
+        elif f.router == "softmax_top":
             rc = L.lp_moe_route_softmax(_lib.ptr(h), h.stride(0), int(h.dtype == F32), T, D, _lib.ptr(lw["w_router"]),
                                         lw["w_router"].stride(0), f.experts, _lib.ptr(lw["router_bias"]), f.top, _lib.ptr(idx),
                                         _lib.ptr(wts), st)
         else:
             rc = L.lp_moe_route(_lib.ptr(h), h.stride(0), int(h.dtype == F32), T, D, _lib.ptr(lw["w_router"]), lw["w_router"].stride(0),
                                 f.experts, _lib.ptr(lw["correction"]), f.n_groups, f.keep_groups, f.top,
-                                _lib.ptr(lw["w_sg"]) if f.shared_ff else None, _lib.ptr(idx), _lib.ptr(wts), _lib.ptr(gate), st)
+                                _lib.ptr(lw["w_sg"]) if gate is not None else None, _lib.ptr(idx), _lib.ptr(wts), _lib.ptr(gate), st)
         self._check(rc, "lp_moe_route")
         n_pairs = T * f.top
         if n_pairs <= MOE_PAIRS_MAX:
@@ -787,14 +963,14 @@ class SeqLMEngine:
             h1 = self._empty((n_pairs, f.expert_ff), self.act)
             d1 = _lib.LinearDesc(A=_lib.ptr(h), lda=h.stride(0), a_batch=0, a_fp32=int(h.dtype == F32), W=_lib.ptr(w_gu), ldw=w_gu.stride(1),
                                  w_batch=w_gu.stride(0), C=_lib.ptr(h1), ldc=h1.stride(0), c_batch=0, c_fp32=int(h1.dtype == F32), M=1,
-                                 N=2 * f.expert_ff, K=D, batch=1, epi=_lib.EPI_SILU_GATE, epi_a=0.0, epi_b=0.0)
+                                 N=2 * f.expert_ff, K=D, batch=1, epi=epi, epi_a=epi_a, epi_b=epi_b, row_scale=_lib.ptr(wts) if on_input else None)
             self._check(L.lp_linear_pairs(C.byref(d1), _lib.ptr(idx), f.top, n_pairs, st), "lp_linear_pairs")
             y = self._empty((n_pairs, D), F32)
             d2 = _lib.LinearDesc(A=_lib.ptr(h1), lda=h1.stride(0), a_batch=0, a_fp32=int(h1.dtype == F32), W=_lib.ptr(w_dn),
                                  ldw=w_dn.stride(1), w_batch=w_dn.stride(0), C=_lib.ptr(y), ldc=y.stride(0), c_batch=0, c_fp32=1, M=1, N=D,
                                  K=f.expert_ff, batch=1, epi=_lib.EPI_NONE, epi_a=0.0, epi_b=0.0)
             self._check(L.lp_linear_pairs(C.byref(d2), _lib.ptr(idx), 1, n_pairs, st), "lp_linear_pairs")
-            return self._moe_combine(f, lw, h, y, self._pair_identity(n_pairs), wts, gate)
+            return self._moe_combine(f, lw, h, y, self._pair_identity(n_pairs), None if on_input else wts, gate)
         tiles = int(L.lp_moe_max_tiles(n_pairs, f.experts, self.tile_rows))
         tile_group = self._empty((tiles,), I32)
         sorted_token = self._empty((tiles * self.tile_rows,), I32)
@@ -803,6 +979,10 @@ class SeqLMEngine:
                             _lib.ptr(pair_row), st)
         self._check(rc, "lp_moe_align")
         rows = tiles * self.tile_rows
+        scale = None
+        if on_input:      # the pairs' weights in the sorted row space
+            scale = self._empty((rows,), F32)
+            self._check(L.lp_moe_sorted_weights(_lib.ptr(pair_row), _lib.ptr(wts), n_pairs, _lib.ptr(scale), st), "lp_moe_sorted_weights")
         h1 = self._empty((rows, f.expert_ff), self.act)
         y = self._empty((rows, D), F32)
         w_gu, w_dn = lw["w_gu"], lw["w_edown"]
@@ -818,19 +998,20 @@ class SeqLMEngine:
                     t1 += 1
                 if e >= 0:
                     r0, r1 = t0 * self.tile_rows, t1 * self.tile_rows
-                    self.linear(a_sorted[r0:r1], w_gu[e], self.act, _lib.EPI_SILU_GATE, out=h1[r0:r1])
+                    self.linear(a_sorted[r0:r1], w_gu[e], self.act, epi, epi_a, epi_b, out=h1[r0:r1],
+                                row_scale=scale[r0:r1] if on_input else None)
                     self.linear(h1[r0:r1], w_dn[e], F32, out=y[r0:r1])
                 t0 = t1
         else:
             d1 = _lib.LinearDesc(A=_lib.ptr(h), lda=h.stride(0), a_batch=0, a_fp32=int(h.dtype == F32), W=_lib.ptr(w_gu), ldw=w_gu.stride(1),
                                  w_batch=w_gu.stride(0), C=_lib.ptr(h1), ldc=h1.stride(0), c_batch=0, c_fp32=int(h1.dtype == F32), M=rows,
-                                 N=2 * f.expert_ff, K=D, batch=1, epi=_lib.EPI_SILU_GATE, epi_a=0.0, epi_b=0.0)
+                                 N=2 * f.expert_ff, K=D, batch=1, epi=epi, epi_a=epi_a, epi_b=epi_b, row_scale=_lib.ptr(scale))
             self._check(L.lp_linear_grouped(C.byref(d1), _lib.ptr(tile_group), tiles, _lib.ptr(sorted_token), st), "lp_linear_grouped")
             d2 = _lib.LinearDesc(A=_lib.ptr(h1), lda=h1.stride(0), a_batch=0, a_fp32=int(h1.dtype == F32), W=_lib.ptr(w_dn),
                                  ldw=w_dn.stride(1), w_batch=w_dn.stride(0), C=_lib.ptr(y), ldc=y.stride(0), c_batch=0, c_fp32=1, M=rows,
                                  N=D, K=f.expert_ff, batch=1, epi=_lib.EPI_NONE, epi_a=0.0, epi_b=0.0)
             self._check(L.lp_linear_grouped(C.byref(d2), _lib.ptr(tile_group), tiles, None, st), "lp_linear_grouped")
-        return self._moe_combine(f, lw, h, y, pair_row, wts, gate)
+        return self._moe_combine(f, lw, h, y, pair_row, None if on_input else wts, gate)
 
     def _pair_identity(self, n: int) -> torch.Tensor:
         t = getattr(self, "_arange", None)
@@ -842,7 +1023,10 @@ class SeqLMEngine:
         T, D = h.shape
         shared = None
         if f.shared_ff:
-            s1 = self.linear(h, lw["ws_gu"], self.act, _lib.EPI_SILU_GATE)
+            if f.act == "clamp_glu":
+                s1 = self.linear(h, lw["ws_gu"], self.act, _lib.EPI_CLAMP_GLU, f.shared_limit, GLU_SLOPE)
+            else:
+                s1 = self.linear(h, lw["ws_gu"], self.act, _lib.EPI_SILU_GATE)
             shared = self.linear(s1, lw["ws_down"], F32)
         out = self._empty((T, D), F32)
         rc = self.L.lp_moe_combine(_lib.ptr(y), y.stride(0), _lib.ptr(pair_row), _lib.ptr(wts), f.top, _lib.ptr(shared),
@@ -904,6 +1088,8 @@ class SeqLMEngine:
             rc = self.L.lp_add_positions_f32(_lib.ptr(x), x.stride(0), b.R, D, _lib.ptr(b.row_pos), _lib.ptr(self.w.position_freq),
                                              self._stream())
             self._check(rc, "lp_add_positions_f32")
+        if cfg.norm == "parallel_dyt":
+            return self._forward_parallel(b, want, x)
         pre = cfg.norm == "pre"
         for li, (lc, lw) in enumerate(zip(cfg.layers, self.w.layers)):
             if self.w.add_before[li] is not None:
@@ -938,9 +1124,57 @@ class SeqLMEngine:
                 self.tap(li, x)
         if want is None:
             return None
+        return self._head(x, want)
+
+    def _head(self, x: torch.Tensor, want) -> torch.Tensor:
         rows = x if isinstance(want, str) else x.index_select(0, want.long())
-        hn = self.norm(rows, self.w.final_gain, self.act)
+        hn = self.dyt(rows, self.w.final_gain)[0] if self.cfg.norm == "parallel_dyt" else self.norm(rows, self.w.final_gain, self.act)
         return self.linear(hn, self.w.head, F32)
+
+    def _forward_parallel(self, b: _Batch, want, x0: torch.Tensor) -> Optional[torch.Tensor]:
+        """Layers whose two sublayers read the SAME stream through two Dynamic-Tanh norms: X' = x + m (gate1 * mixer(norm1 x) + gate2 *
+        ff(norm2 x)).  With the depth average the results X_0 (the embedding), X_1, ... are kept ([layers + 1, rows, width] fp32) and
+        the next layer reads their weighted sum; the branches are added into the slot of X' in the stores of their last products."""
+        cfg, D, R, st = self.cfg, self.cfg.width, b.R, self._stream()
+        n_layers = len(cfg.layers)
+        if cfg.depth_average:
+            hist = self._empty((n_layers + 1, R, D), F32)
+            hist[0].copy_(x0)
+            x = x0
+        else:
+            x = x0
+        for li, (lc, lw) in enumerate(zip(cfg.layers, self.w.layers)):
+            if cfg.depth_average:      # the slot of this layer's result starts as its input
+                acc = hist[li + 1]
+                if li == 0:
+                    acc.copy_(x)
+            else:
+                acc = x
+            h1, h2 = self.dyt(x, lw["norm1"], lw["norm2"] if lc.ff is not None else None)
+            g1 = self.linear(h1, lw["w_rg1"], F32, bias=lw["rg1_bias"]) if cfg.residual_gate else None
+            g2 = self.linear(h2, lw["w_rg2"], F32, bias=lw["rg2_bias"]) if cfg.residual_gate and lc.ff is not None else None
+            # both operands exist before anything is added, so `acc` may be the stream itself
+            self._mix(li, lc.mixer, lw, h1, b, into=(acc, cfg.residual_mult, g1) if g1 is not None else (acc, cfg.residual_mult))
+            if isinstance(lc.ff, DenseFFConfig):
+                self._dense(lc.ff, lw, h2, into=(acc, cfg.residual_mult, g2) if g2 is not None else (acc, cfg.residual_mult))
+            elif lc.ff is not None:
+                y = self._moe(lc.ff, lw, h2)
+                rc = self.L.lp_gated_axpy_f32(_lib.ptr(acc), acc.stride(0), _lib.ptr(y), y.stride(0), None, _lib.ptr(g2),
+                                              g2.stride(0) if g2 is not None else 0, None, cfg.residual_mult, R, D, st)
+                self._check(rc, "lp_gated_axpy_f32")
+            if cfg.depth_average:
+                x = self._empty((R, D), F32)
+                nxt = hist[li + 2] if li + 1 < n_layers else None
+                rc = self.L.lp_depth_average_f32(_lib.ptr(hist), hist.stride(0), hist.stride(1), _lib.ptr(lw["dwa"]), li + 2, _lib.ptr(x),
+                                                 x.stride(0), _lib.ptr(nxt), nxt.stride(0) if nxt is not None else 0, R, D, st)
+                self._check(rc, "lp_depth_average_f32")
+            else:
+                x = acc
+            if self.tap is not None:
+                self.tap(li, x)
+        if want is None:
+            return None
+        return self._head(x, want)
 
     def finish(self, key: Hashable) -> None:
         """The request is over: its pages and its slot go back to the pools."""
