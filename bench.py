@@ -568,11 +568,11 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg3", choices=["cfg3", "cfg2", "cfg4", "cfg5", "seqlm", "ronelorn", "gavatar"],
+    ap.add_argument("--workload", default="cfg3", choices=["cfg3", "cfg2", "cfg4", "cfg5", "seqlm", "ronelorn", "gavatar", "kamosun"],
                     help="cfg3 (default) = the metric's configuration; cfg2 = 1 x 1344^2; cfg4 = Idefics2 8 x 980^2; cfg5 = SFT step; "
                          "seqlm = prefill / decode of the layer-list language models beside the Llama-style decoder at equal size; "
-                         "ronelorn = the same for the Ronelorn layers beside the Zudalorn stack at equal size; gavatar = the same for the Gavatar layers")
-    ap.add_argument("--seqlm-sizes", default="", help="seqlm / ronelorn / gavatar: comma-separated subset of w1024,w2048,w4096 (default: all three)")
+                         "ronelorn = the same for the Ronelorn layers beside the Zudalorn stack at equal size; gavatar = the same for the Gavatar layers; kamosun = the same for the Kamosun layers")
+    ap.add_argument("--seqlm-sizes", default="", help="seqlm / ronelorn / gavatar / kamosun: comma-separated subset of w1024,w2048,w4096 (default: all three)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the library / strong-scaling / decode / front-end legs")
     ap.add_argument("--quick", action="store_true", help="1 warm-up, timed loop only (for runs under ncu)")
@@ -596,6 +596,9 @@ def main():
     if args.workload == "gavatar":
         from benchmarks import gavatar_bench
         return gavatar_bench.run(args)
+    if args.workload == "kamosun":
+        from benchmarks import kamosun_bench
+        return kamosun_bench.run(args)
     if args.workload in ("cfg4", "cfg5"):
         from benchmarks import other_workloads
         return other_workloads.run(args)

@@ -116,40 +116,100 @@ __global__ void glu_kernel(const IT* __restrict__ in, long long ldi, OT* __restr
   st32(out + (long long)m * ldo + n, v);
 }
 
-template <typename OT>
+// The three elementwise kernels below work on groups of V consecutive columns per thread: V = 4 (16-byte fp32 accesses, 8-byte bf16
+// stores) when the width and every row stride and base allow it, else V = 1.
+template <int V> struct f32vec;
+template <> struct f32vec<1> { float v[1]; };
+template <> struct alignas(16) f32vec<4> { float v[4]; };
+template <int V> __device__ __forceinline__ f32vec<V> ldv(const float* p) { return *reinterpret_cast<const f32vec<V>*>(p); }
+template <int V> __device__ __forceinline__ void stv(float* p, const f32vec<V>& x) { *reinterpret_cast<f32vec<V>*>(p) = x; }
+template <int V> __device__ __forceinline__ void stv(bf16* p, const f32vec<V>& x) {
+  if constexpr (V == 4) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(x.v[0], x.v[1]), hi = __floats2bfloat162_rn(x.v[2], x.v[3]);
+    uint2 u;
+    u.x = *reinterpret_cast<const unsigned*>(&lo);
+    u.y = *reinterpret_cast<const unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+  } else {
+    *p = __float2bfloat16(x.v[0]);
+  }
+}
+
+template <typename OT, int V>
 __global__ void dyt_f32_kernel(const float* __restrict__ x, long long ldx, int M, int D, float alpha, const float* __restrict__ gain,
                                const float* __restrict__ shift, OT* __restrict__ out, long long ldo, float alpha2,
                                const float* __restrict__ gain2, const float* __restrict__ shift2, OT* __restrict__ out2, long long ldo2) {
+  const int DV = D / V;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (long long)M * D) return;
-  const int m = (int)(i / D), c = (int)(i % D);
-  const float v = x[(long long)m * ldx + c];
-  st32(out + (long long)m * ldo + c, fmaf(tanhf(alpha * v), gain[c], shift != nullptr ? shift[c] : 0.f));
-  if (out2 != nullptr) st32(out2 + (long long)m * ldo2 + c, fmaf(tanhf(alpha2 * v), gain2[c], shift2 != nullptr ? shift2[c] : 0.f));
+  if (i >= (long long)M * DV) return;
+  const int m = (int)(i / DV), c = (int)(i % DV) * V;
+  const f32vec<V> v = ldv<V>(x + (long long)m * ldx + c);
+  f32vec<V> y;
+  {
+    const f32vec<V> g = ldv<V>(gain + c);
+#pragma unroll
+    for (int k = 0; k < V; ++k) y.v[k] = fmaf(tanhf(alpha * v.v[k]), g.v[k], shift != nullptr ? shift[c + k] : 0.f);
+    stv<V>(out + (long long)m * ldo + c, y);
+  }
+  if (out2 != nullptr) {
+    const f32vec<V> g = ldv<V>(gain2 + c);
+#pragma unroll
+    for (int k = 0; k < V; ++k) y.v[k] = fmaf(tanhf(alpha2 * v.v[k]), g.v[k], shift2 != nullptr ? shift2[c + k] : 0.f);
+    stv<V>(out2 + (long long)m * ldo2 + c, y);
+  }
 }
 
+template <int V>
 __global__ void gated_axpy_f32_kernel(float* __restrict__ x, long long ldx, const float* __restrict__ y, long long ldy,
                                       const float* __restrict__ y_bias, const float* __restrict__ g, long long ldg,
                                       const float* __restrict__ g_bias, float mult, int M, int N) {
+  const int NV = N / V;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (long long)M * N) return;
-  const int m = (int)(i / N), n = (int)(i % N);
-  float v = y[(long long)m * ldy + n] + (y_bias != nullptr ? y_bias[n] : 0.f);
-  if (g != nullptr) v /= 1.0f + expf(-(g[(long long)m * ldg + n] + (g_bias != nullptr ? g_bias[n] : 0.f)));
-  x[(long long)m * ldx + n] = fmaf(mult, v, x[(long long)m * ldx + n]);
+  if (i >= (long long)M * NV) return;
+  const int m = (int)(i / NV), n = (int)(i % NV) * V;
+  f32vec<V> acc = ldv<V>(x + (long long)m * ldx + n);
+  const f32vec<V> yv = ldv<V>(y + (long long)m * ldy + n);
+  f32vec<V> gv;
+  if (g != nullptr) gv = ldv<V>(g + (long long)m * ldg + n);
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    float v = yv.v[k] + (y_bias != nullptr ? y_bias[n + k] : 0.f);
+    if (g != nullptr) v /= 1.0f + expf(-(gv.v[k] + (g_bias != nullptr ? g_bias[n + k] : 0.f)));
+    acc.v[k] = fmaf(mult, v, acc.v[k]);
+  }
+  stv<V>(x + (long long)m * ldx + n, acc);
 }
 
+template <int V>
 __global__ void depth_average_f32_kernel(const float* __restrict__ hist, long long layer_stride, long long ldh,
                                          const float* __restrict__ coef, int n, float* __restrict__ out, long long ldo,
                                          float* __restrict__ copy, long long ldc, int M, int N) {
+  const int NV = N / V;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (long long)M * N) return;
-  const int m = (int)(i / N), c = (int)(i % N);
+  if (i >= (long long)M * NV) return;
+  const int m = (int)(i / NV), c = (int)(i % NV) * V;
   const float* src = hist + (long long)m * ldh + c;
-  float acc = 0.f;
-  for (int j = 0; j < n; ++j) acc = fmaf(coef[j], src[(long long)j * layer_stride], acc);
-  out[(long long)m * ldo + c] = acc;
-  if (copy != nullptr) copy[(long long)m * ldc + c] = acc;
+  f32vec<V> acc;
+#pragma unroll
+  for (int k = 0; k < V; ++k) acc.v[k] = 0.f;
+  for (int j = 0; j < n; ++j) {
+    const f32vec<V> h = ldv<V>(src + (long long)j * layer_stride);
+    const float cj = coef[j];
+#pragma unroll
+    for (int k = 0; k < V; ++k) acc.v[k] = fmaf(cj, h.v[k], acc.v[k]);
+  }
+  stv<V>(out + (long long)m * ldo + c, acc);
+  if (copy != nullptr) stv<V>(copy + (long long)m * ldc + c, acc);
+}
+
+// 16-byte accesses need every base on a 16-byte boundary and every row stride a multiple of four floats
+static bool vec4_ok(int N, std::initializer_list<const void*> bases, std::initializer_list<long long> strides) {
+  if (N % 4) return false;
+  for (const void* b : bases)
+    if (b != nullptr && (reinterpret_cast<uintptr_t>(b) & 15)) return false;
+  for (long long s : strides)
+    if (s % 4) return false;
+  return true;
 }
 
 __global__ void axpy_f32_kernel(float* __restrict__ y, long long ldy, const float* __restrict__ x, long long ldx, float alpha, int M, int N) {
@@ -312,13 +372,21 @@ extern "C" int lp_dyt_f32(const float* x, long long ldx, int M, int D, float alp
   LP_REQUIRE(x != nullptr && gain != nullptr && out != nullptr && M >= 0 && D > 0, "lp_dyt_f32: bad arguments");
   LP_REQUIRE(out2 == nullptr || gain2 != nullptr, "lp_dyt_f32: a second output without its gain");
   if (M == 0) return 0;
-  const unsigned grid = (unsigned)(((long long)M * D + 255) / 256);
-  if (out_fp32)
-    dyt_f32_kernel<float><<<grid, 256, 0, stream>>>(x, ldx, M, D, alpha, gain, shift, reinterpret_cast<float*>(out), ldo, alpha2, gain2, shift2,
-                                                    reinterpret_cast<float*>(out2), ldo2);
+  // bf16 rows of four are 8 bytes: their bases need 8-byte alignment, which the 16-byte test covers
+  const bool v4 = vec4_ok(D, {x, gain, gain2, out, out2}, {ldx, ldo, out2 != nullptr ? ldo2 : 0});
+  const unsigned grid = (unsigned)(((long long)M * (v4 ? D / 4 : D) + 255) / 256);
+  if (out_fp32 && v4)
+    dyt_f32_kernel<float, 4><<<grid, 256, 0, stream>>>(x, ldx, M, D, alpha, gain, shift, reinterpret_cast<float*>(out), ldo, alpha2, gain2,
+                                                       shift2, reinterpret_cast<float*>(out2), ldo2);
+  else if (out_fp32)
+    dyt_f32_kernel<float, 1><<<grid, 256, 0, stream>>>(x, ldx, M, D, alpha, gain, shift, reinterpret_cast<float*>(out), ldo, alpha2, gain2,
+                                                       shift2, reinterpret_cast<float*>(out2), ldo2);
+  else if (v4)
+    dyt_f32_kernel<bf16, 4><<<grid, 256, 0, stream>>>(x, ldx, M, D, alpha, gain, shift, reinterpret_cast<bf16*>(out), ldo, alpha2, gain2,
+                                                      shift2, reinterpret_cast<bf16*>(out2), ldo2);
   else
-    dyt_f32_kernel<bf16><<<grid, 256, 0, stream>>>(x, ldx, M, D, alpha, gain, shift, reinterpret_cast<bf16*>(out), ldo, alpha2, gain2, shift2,
-                                                   reinterpret_cast<bf16*>(out2), ldo2);
+    dyt_f32_kernel<bf16, 1><<<grid, 256, 0, stream>>>(x, ldx, M, D, alpha, gain, shift, reinterpret_cast<bf16*>(out), ldo, alpha2, gain2,
+                                                      shift2, reinterpret_cast<bf16*>(out2), ldo2);
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
   return 0;
@@ -344,7 +412,10 @@ extern "C" int lp_gated_axpy_f32(float* x, long long ldx, const float* y, long l
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LP_REQUIRE(x != nullptr && y != nullptr && M >= 0 && N > 0, "lp_gated_axpy_f32: bad arguments");
   if (M == 0) return 0;
-  gated_axpy_f32_kernel<<<(unsigned)(((long long)M * N + 255) / 256), 256, 0, stream>>>(x, ldx, y, ldy, y_bias, g, ldg, g_bias, mult, M, N);
+  if (vec4_ok(N, {x, y, g}, {ldx, ldy, g != nullptr ? ldg : 0}))
+    gated_axpy_f32_kernel<4><<<(unsigned)(((long long)M * (N / 4) + 255) / 256), 256, 0, stream>>>(x, ldx, y, ldy, y_bias, g, ldg, g_bias, mult, M, N);
+  else
+    gated_axpy_f32_kernel<1><<<(unsigned)(((long long)M * N + 255) / 256), 256, 0, stream>>>(x, ldx, y, ldy, y_bias, g, ldg, g_bias, mult, M, N);
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
   return 0;
@@ -355,8 +426,12 @@ extern "C" int lp_depth_average_f32(const float* hist, long long layer_stride, l
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LP_REQUIRE(hist != nullptr && coef != nullptr && out != nullptr && n > 0 && M >= 0 && N > 0, "lp_depth_average_f32: bad arguments");
   if (M == 0) return 0;
-  depth_average_f32_kernel<<<(unsigned)(((long long)M * N + 255) / 256), 256, 0, stream>>>(hist, layer_stride, ldh, coef, n, out, ldo, copy,
-                                                                                         ldc, M, N);
+  if (vec4_ok(N, {hist, out, copy}, {layer_stride, ldh, ldo, copy != nullptr ? ldc : 0}))
+    depth_average_f32_kernel<4><<<(unsigned)(((long long)M * (N / 4) + 255) / 256), 256, 0, stream>>>(hist, layer_stride, ldh, coef, n, out, ldo,
+                                                                                                    copy, ldc, M, N);
+  else
+    depth_average_f32_kernel<1><<<(unsigned)(((long long)M * N + 255) / 256), 256, 0, stream>>>(hist, layer_stride, ldh, coef, n, out, ldo,
+                                                                                              copy, ldc, M, N);
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -249,6 +249,11 @@ class SeqLMConfig:
     depth_average: bool = False
 
 
+# the weight of every mixer's first product of its operand (SeqLMWeights)
+FIRST_PRODUCT = {RetentionConfig: "w_qkvg", LatentAttentionConfig: "w_qdkv", WindowAttentionConfig: "w_qkv", MinGRUConfig: "w_zxg",
+                 MLSTMConfig: "w_proj"}
+
+
 def softplus(x: float) -> float:
     return math.log1p(math.exp(-abs(x))) + max(x, 0.0)
 
@@ -420,6 +425,20 @@ class SeqLMWeights:
                 lw.update(mixer_weights(m, "mix."))
             if cfg.residual_gate:
                 lw["w_rg1"], lw["rg1_bias"] = mat(w(i, "rg1", (D, D))), vec(w(i, "rg1.b", (D,)))
+                # the mixer's first projections and its gate read the same operand: one weight [projections | gate] and one product;
+                # the tensors above become row ranges of it
+                owners = ([(lw["left"], FIRST_PRODUCT[type(m.left)]), (lw["right"], FIRST_PRODUCT[type(m.right)])]
+                          if isinstance(m, ParallelMixerConfig) else [(lw, FIRST_PRODUCT[type(m)])])
+                fused = torch.cat([o[k] for o, k in owners] + [lw["w_rg1"]], 0).contiguous()
+                at, split = 0, []
+                for o, k in owners:
+                    n = o[k].shape[0]
+                    o[k] = fused[at:at + n]
+                    split.append((at, n))
+                    at += n
+                lw["w_rg1"] = fused[at:]
+                lw["w_in"], lw["in_split"] = fused, split
+                lw["in_bias"] = torch.cat([torch.zeros(at, dtype=F32, device=dev), lw["rg1_bias"]]).contiguous()
                 if lc.ff is not None:
                     lw["w_rg2"], lw["rg2_bias"] = mat(w(i, "rg2", (D, D))), vec(w(i, "rg2.b", (D,)))
             if cfg.depth_average:
@@ -750,8 +769,8 @@ class SeqLMEngine:
         return out, out2
 
     # ------------------------------------------------------------------ mixers
-    def _retention(self, li: int, m: RetentionConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
-        qkvg = self.linear(h, lw["w_qkvg"], F32)
+    def _retention(self, li, m: RetentionConfig, lw, h: torch.Tensor, b: _Batch, into=None, proj=None) -> torch.Tensor:
+        qkvg = proj if proj is not None else self.linear(h, lw["w_qkvg"], F32)
         hd, hv = m.heads * m.dim, m.heads * m.vdim
         lightning = m.form == "lightning"      # the raw read-out in fp32; its norm spans the heads and follows below
         out = self._empty((b.R, hv), F32 if lightning else self.act)
@@ -781,9 +800,9 @@ class SeqLMEngine:
             out = normed
         return self.linear(out, lw["w_o"], F32, into=into)
 
-    def _latent(self, li: int, m: LatentAttentionConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
+    def _latent(self, li, m: LatentAttentionConfig, lw, h: torch.Tensor, b: _Batch, into=None, proj=None) -> torch.Tensor:
         per = m.dim + m.rot_dim
-        qd = self.linear(h, lw["w_qdkv"], F32)
+        qd = proj if proj is not None else self.linear(h, lw["w_qdkv"], F32)
         nq = m.q_rank or m.heads * per
         dkv = qd[:, nq: nq + m.kv_rank + m.rot_dim]
         gate = qd[:, nq + m.kv_rank + m.rot_dim:] if m.head_gate else None
@@ -810,8 +829,8 @@ class SeqLMEngine:
         self.linear_heads(lat, m.kv_rank, lw["w_uv"].view(m.heads, m.vdim, m.kv_rank), o, m.vdim)
         return self.linear(o, lw["w_o"], F32, into=into)
 
-    def _window_attention(self, li: int, m: WindowAttentionConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
-        qkv = self.linear(h, lw["w_qkv"], F32)      # a layer that reads another layer's keys and values projects its queries only
+    def _window_attention(self, li, m: WindowAttentionConfig, lw, h: torch.Tensor, b: _Batch, into=None, proj=None) -> torch.Tensor:
+        qkv = proj if proj is not None else self.linear(h, lw["w_qkv"], F32)      # a layer that reads another layer's keys and values projects its queries only
         hq, hk = m.heads * m.dim, m.kv_heads * m.dim if m.kv_from is None else 0
         cache = self.cache
         pool = cache.pools[self._cache_index[li]]
@@ -861,8 +880,8 @@ class SeqLMEngine:
         self._check(rc, "lp_window_attn")
         return self.linear(o, lw["w_o"], F32, into=into, bias=lw.get("o_bias"))
 
-    def _mingru(self, li: int, m: MinGRUConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
-        zxg = self.linear(h, lw["w_zxg"], F32)
+    def _mingru(self, li, m: MinGRUConfig, lw, h: torch.Tensor, b: _Batch, into=None, proj=None) -> torch.Tensor:
+        zxg = proj if proj is not None else self.linear(h, lw["w_zxg"], F32)
         out = self._empty((b.R, m.width), self.act)
         state = self.cache.states[self._state_index[li]]
         d = _lib.MinGRUDesc(zxg=_lib.ptr(zxg), ld=zxg.stride(0), z_off=0, x_off=m.width, g_off=2 * m.width, width=m.width,
@@ -880,8 +899,8 @@ class SeqLMEngine:
             self._check(rc, "lp_mingru_prefill")
         return self.linear(out, lw["w_o"], F32, into=into)
 
-    def _mlstm(self, li: int, m: MLSTMConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
-        proj = self.linear(h, lw["w_proj"], F32)
+    def _mlstm(self, li, m: MLSTMConfig, lw, h: torch.Tensor, b: _Batch, into=None, proj=None) -> torch.Tensor:
+        proj = proj if proj is not None else self.linear(h, lw["w_proj"], F32)
         hd, hv = m.heads * m.dim, m.heads * m.vdim
         out = self._empty((b.R, hv), self.act)
         state = self.cache.states[self._state_index[li]]
@@ -897,10 +916,11 @@ class SeqLMEngine:
         self._check(rc, "lp_mlstm")
         return self.linear(out, lw["w_o"], F32, into=into)
 
-    def _parallel(self, li: int, m: ParallelMixerConfig, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
-        """two mixers on the same input; each output is RMS-normed over the width with its own gain (which carries the halving)"""
-        left = self._mix((li, "left"), m.left, lw["left"], h, b)
-        right = self._mix((li, "right"), m.right, lw["right"], h, b)
+    def _parallel(self, li: int, m: ParallelMixerConfig, lw, h: torch.Tensor, b: _Batch, into=None, proj=None) -> torch.Tensor:
+        """two mixers on the same input; each output is RMS-normed over the width with its own gain (which carries the halving);
+        proj: the two branches' first products when one product of the layer made them"""
+        left = self._mix((li, "left"), m.left, lw["left"], h, b, proj=proj[0] if proj is not None else None)
+        right = self._mix((li, "right"), m.right, lw["right"], h, b, proj=proj[1] if proj is not None else None)
         mix = self.norm(left, lw["left_out"], F32)
         self.norm(right, lw["right_out"], accum=mix)
         if into is None:
@@ -912,19 +932,20 @@ class SeqLMEngine:
         self._check(rc, "lp_gated_axpy_f32")
         return x
 
-    def _mix(self, li, m, lw, h: torch.Tensor, b: _Batch, into=None) -> torch.Tensor:
-        """li: the key of the mixer's cache and state — the layer, or (layer, side) for a branch of a parallel mixer"""
+    def _mix(self, li, m, lw, h: torch.Tensor, b: _Batch, into=None, proj=None) -> torch.Tensor:
+        """li: the key of the mixer's cache and state — the layer, or (layer, side) for a branch of a parallel mixer; proj: the
+        mixer's first product of h (fp32, possibly columns of a wider product) when the caller has made it already"""
         if isinstance(m, ParallelMixerConfig):
-            return self._parallel(li, m, lw, h, b, into)
+            return self._parallel(li, m, lw, h, b, into, proj)
         if isinstance(m, MLSTMConfig):
-            return self._mlstm(li, m, lw, h, b, into)
+            return self._mlstm(li, m, lw, h, b, into, proj)
         if isinstance(m, RetentionConfig):
-            return self._retention(li, m, lw, h, b, into)
+            return self._retention(li, m, lw, h, b, into, proj)
         if isinstance(m, LatentAttentionConfig):
-            return self._latent(li, m, lw, h, b, into)
+            return self._latent(li, m, lw, h, b, into, proj)
         if isinstance(m, WindowAttentionConfig):
-            return self._window_attention(li, m, lw, h, b, into)
-        return self._mingru(li, m, lw, h, b, into)
+            return self._window_attention(li, m, lw, h, b, into, proj)
+        return self._mingru(li, m, lw, h, b, into, proj)
 
     # ------------------------------------------------------------------ feed-forwards
     def _dense(self, f: DenseFFConfig, lw, h: torch.Tensor, into=None) -> torch.Tensor:
@@ -1151,10 +1172,17 @@ class SeqLMEngine:
             else:
                 acc = x
             h1, h2 = self.dyt(x, lw["norm1"], lw["norm2"] if lc.ff is not None else None)
-            g1 = self.linear(h1, lw["w_rg1"], F32, bias=lw["rg1_bias"]) if cfg.residual_gate else None
+            g1 = proj = None
+            if "w_in" in lw:      # ONE product of h1: every branch's first projection and the pre-activations of the mixer's gate
+                wide = self.linear(h1, lw["w_in"], F32, bias=lw["in_bias"])
+                parts = [wide[:, a:a + n] for a, n in lw["in_split"]]
+                proj = tuple(parts) if isinstance(lc.mixer, ParallelMixerConfig) else parts[0]
+                g1 = wide[:, wide.shape[1] - D:]
+            elif cfg.residual_gate:
+                g1 = self.linear(h1, lw["w_rg1"], F32, bias=lw["rg1_bias"])
             g2 = self.linear(h2, lw["w_rg2"], F32, bias=lw["rg2_bias"]) if cfg.residual_gate and lc.ff is not None else None
             # both operands exist before anything is added, so `acc` may be the stream itself
-            self._mix(li, lc.mixer, lw, h1, b, into=(acc, cfg.residual_mult, g1) if g1 is not None else (acc, cfg.residual_mult))
+            self._mix(li, lc.mixer, lw, h1, b, into=(acc, cfg.residual_mult, g1) if g1 is not None else (acc, cfg.residual_mult), proj=proj)
             if isinstance(lc.ff, DenseFFConfig):
                 self._dense(lc.ff, lw, h2, into=(acc, cfg.residual_mult, g2) if g2 is not None else (acc, cfg.residual_mult))
             elif lc.ff is not None:

@@ -188,3 +188,81 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, taps: Optional[list] 
         if taps is not None:
             taps.append(x.clone())
     return dynamic_tanh(x, w, "final.norm") @ w["head"].T
+
+
+def random_weights(cfg: dict, seed: int = 0, scale: float = 1.0) -> Dict[str, torch.Tensor]:
+    """bf16-representable random tensors under the checkpoint's names"""
+    gen = torch.Generator().manual_seed(seed)
+    D = cfg["width"]
+    out: Dict[str, torch.Tensor] = {}
+
+    def mat(name, n, k, s=1.0):
+        out[name] = (torch.randn(n, k, generator=gen) * s * scale / math.sqrt(k)).to(torch.bfloat16).float()
+
+    def vec(name, n, s=0.3, mean=0.0):
+        out[name] = (torch.randn(n, generator=gen) * s + mean).to(torch.bfloat16).float()
+
+    def dyt(name):
+        vec(name, D, mean=1.0)
+        vec(name + ".b", D, s=0.2)
+        out[name + ".alpha"] = (torch.rand((), generator=gen) * 0.8 + 0.4).to(torch.bfloat16).float()
+
+    def glu(p, ff):
+        mat(p + "gate", ff, D, 2.0)
+        mat(p + "up", ff, D, 2.0)
+        mat(p + "down", D, ff)
+
+    def attention(p, m, bias):
+        H, d, e = m["heads"], m["dim"], m.get("vdim", m["dim"])
+        G = m.get("kv_heads", H)
+        own = m.get("kv_from") is None
+        for k, n in (("q", H * d), ("k", G * d), ("v", G * e)):
+            if k == "q" or own:
+                mat(p + k, n, D)
+                if bias:
+                    vec(p + k + ".b", n)
+        vec(p + "q.norm", d, mean=1.0)
+        if own:
+            vec(p + "k.norm", d, mean=1.0)
+        mat(p + "o", D, H * e)
+        if bias:
+            vec(p + "o.b", D)
+
+    mat("embed", cfg["vocab"], D, math.sqrt(D))
+    mat("head", cfg["vocab"], D)
+    dyt("final.norm")
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        dyt(p + "norm1")
+        mat(p + "rg1", D, D)
+        vec(p + "rg1.b", D, s=0.5)
+        out[p + "dwa"] = (torch.randn(i + 2, generator=gen) * 0.3 + torch.tensor([0.0] * (i + 1) + [1.0])).to(torch.bfloat16).float()
+        if layer["type"] == "attention":
+            attention(p + "mix.", m, True)
+        elif layer["type"] == "parallel":
+            attention(p + "mix.left.", m["left"], False)
+            r = m["right"]
+            H, d, e = r["heads"], r["dim"], r.get("vdim", r["dim"])
+            for k, n in (("q", H * d), ("k", H * d), ("v", H * e), ("g", H * e)):
+                mat(p + "mix.right." + k, n, D, 2.0)
+            mat(p + "mix.right.o", D, H * e)
+            vec(p + "mix.right.norm", H * e, mean=1.0)
+            vec(p + "mix.left.out", D, mean=1.0)
+            vec(p + "mix.right.out", D, mean=1.0)
+        else:
+            raise ValueError(layer["type"])
+        f = layer.get("mlp")
+        if f is None:
+            continue
+        dyt(p + "norm2")
+        mat(p + "rg2", D, D)
+        vec(p + "rg2.b", D, s=0.5)
+        if f["kind"] == "dense":
+            glu(p + "mlp.", f["ff"])
+        else:
+            mat(p + "mlp.router", f["router"]["experts"], D, 3.0)
+            for e_ in range(f["router"]["experts"]):
+                glu(f"{p}mlp.e{e_}.", f["expert"]["ff"])
+            if f.get("shared"):
+                glu(p + "mlp.shared.", f["shared"]["ff"])
+    return out
