@@ -1002,7 +1002,7 @@ class SeqLMEngine:
         rows = tiles * self.tile_rows
         scale = None
         if on_input:      # the pairs' weights in the sorted row space
-            scale = self._empty((rows,), F32)
+            scale = torch.zeros((rows,), dtype=F32, device=self.device)      # padding rows of the sorted space stay zero
             self._check(L.lp_moe_sorted_weights(_lib.ptr(pair_row), _lib.ptr(wts), n_pairs, _lib.ptr(scale), st), "lp_moe_sorted_weights")
         h1 = self._empty((rows, f.expert_ff), self.act)
         y = self._empty((rows, D), F32)
