@@ -135,6 +135,16 @@ template <int V> __device__ __forceinline__ void stv(bf16* p, const f32vec<V>& x
   }
 }
 
+// tanh for an output that is rounded to bf16 (8 bits of mantissa): 1 - 2 / (e^(2|x|) + 1) on the fast exponential and division
+// (absolute error of a few 1e-7, far below the rounding that follows); the fp32 output keeps the accurate tanhf
+template <typename OT> __device__ __forceinline__ float dyt_tanh(float x);
+template <> __device__ __forceinline__ float dyt_tanh<float>(float x) { return tanhf(x); }
+template <> __device__ __forceinline__ float dyt_tanh<bf16>(float x) {
+  const float a = fminf(fabsf(x), 15.f);      // tanh(15) rounds to 1 in fp32; the bound keeps the exponential finite
+  const float t = 1.0f - __fdividef(2.0f, __expf(2.0f * a) + 1.0f);
+  return copysignf(t, x);
+}
+
 template <typename OT, int V>
 __global__ void dyt_f32_kernel(const float* __restrict__ x, long long ldx, int M, int D, float alpha, const float* __restrict__ gain,
                                const float* __restrict__ shift, OT* __restrict__ out, long long ldo, float alpha2,
@@ -148,13 +158,13 @@ __global__ void dyt_f32_kernel(const float* __restrict__ x, long long ldx, int M
   {
     const f32vec<V> g = ldv<V>(gain + c);
 #pragma unroll
-    for (int k = 0; k < V; ++k) y.v[k] = fmaf(tanhf(alpha * v.v[k]), g.v[k], shift != nullptr ? shift[c + k] : 0.f);
+    for (int k = 0; k < V; ++k) y.v[k] = fmaf(dyt_tanh<OT>(alpha * v.v[k]), g.v[k], shift != nullptr ? shift[c + k] : 0.f);
     stv<V>(out + (long long)m * ldo + c, y);
   }
   if (out2 != nullptr) {
     const f32vec<V> g = ldv<V>(gain2 + c);
 #pragma unroll
-    for (int k = 0; k < V; ++k) y.v[k] = fmaf(tanhf(alpha2 * v.v[k]), g.v[k], shift2 != nullptr ? shift2[c + k] : 0.f);
+    for (int k = 0; k < V; ++k) y.v[k] = fmaf(dyt_tanh<OT>(alpha2 * v.v[k]), g.v[k], shift2 != nullptr ? shift2[c + k] : 0.f);
     stv<V>(out2 + (long long)m * ldo2 + c, y);
   }
 }

@@ -69,6 +69,7 @@ inline float2 __bfloat1622float2(__nv_bfloat162 v) { return {(float)v.x, (float)
 
 // ---- math ------------------------------------------------------------------------------------------------------------
 inline float __expf(float x) { return std::exp(x); }
+inline float __fdividef(float a, float b) { return a / b; }
 inline float rsqrtf(float x) { return 1.0f / std::sqrt(x); }
 using std::min;
 using std::max;
