@@ -289,6 +289,8 @@ class SeqLMWeights:
             raise ValueError(f"unknown norm style {cfg.norm!r}")
         pre = cfg.norm == "pre"
         dyt = cfg.norm == "parallel_dyt"
+        if (cfg.residual_gate or cfg.depth_average) and not dyt:
+            raise ValueError("gated residual branches and the depth average belong to the parallel layer form")
         vector = cfg.norm != "sandwich"
 
         def dyt_norm(layer, key):           # (alpha, gain, shift) of a Dynamic Tanh
@@ -1101,7 +1103,10 @@ class SeqLMEngine:
     def _forward(self, b: _Batch, want) -> Optional[torch.Tensor]:
         """embedding -> layers -> (final norm, head) over the rows `want` (a device index tensor, "all", or None)"""
         cfg, D = self.cfg, self.cfg.width
-        x = self._empty((b.R, D), F32)
+        hist = None
+        if cfg.depth_average:      # every layer's result is kept: the embedding output is the first of them
+            hist = self._empty((len(cfg.layers) + 1, b.R, D), F32)
+        x = hist[0] if hist is not None else self._empty((b.R, D), F32)
         rc = self.L.lp_embed_rows_f32(_lib.ptr(b.tokens), b.R, _lib.ptr(self.w.embed), self.w.embed.stride(0), cfg.vocab, cfg.embed_scale,
                                       _lib.ptr(x), x.stride(0), D, self._stream())
         self._check(rc, "lp_embed_rows_f32")
@@ -1110,7 +1115,7 @@ class SeqLMEngine:
                                              self._stream())
             self._check(rc, "lp_add_positions_f32")
         if cfg.norm == "parallel_dyt":
-            return self._forward_parallel(b, want, x)
+            return self._forward_parallel(b, want, x, hist)
         pre = cfg.norm == "pre"
         for li, (lc, lw) in enumerate(zip(cfg.layers, self.w.layers)):
             if self.w.add_before[li] is not None:
@@ -1152,18 +1157,14 @@ class SeqLMEngine:
         hn = self.dyt(rows, self.w.final_gain)[0] if self.cfg.norm == "parallel_dyt" else self.norm(rows, self.w.final_gain, self.act)
         return self.linear(hn, self.w.head, F32)
 
-    def _forward_parallel(self, b: _Batch, want, x0: torch.Tensor) -> Optional[torch.Tensor]:
+    def _forward_parallel(self, b: _Batch, want, x0: torch.Tensor, hist: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Layers whose two sublayers read the SAME stream through two Dynamic-Tanh norms: X' = x + m (gate1 * mixer(norm1 x) + gate2 *
         ff(norm2 x)).  With the depth average the results X_0 (the embedding), X_1, ... are kept ([layers + 1, rows, width] fp32) and
-        the next layer reads their weighted sum; the branches are added into the slot of X' in the stores of their last products."""
+        the next layer reads their weighted sum; the branches are added into the slot of X' in the stores of their last products.
+        x0: the embedding output, which is hist[0] when there is a depth average."""
         cfg, D, R, st = self.cfg, self.cfg.width, b.R, self._stream()
         n_layers = len(cfg.layers)
-        if cfg.depth_average:
-            hist = self._empty((n_layers + 1, R, D), F32)
-            hist[0].copy_(x0)
-            x = x0
-        else:
-            x = x0
+        x = x0
         for li, (lc, lw) in enumerate(zip(cfg.layers, self.w.layers)):
             if cfg.depth_average:      # the slot of this layer's result starts as its input
                 acc = hist[li + 1]

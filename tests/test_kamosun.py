@@ -382,3 +382,69 @@ def test_registry_and_config_reader():
     bad["layers"][1]["mixer"]["kv_from"] = 2                  # not an earlier attention layer with keys of its own
     with pytest.raises(ValueError):
         make_engine(bad, O.random_weights(mixed_model(), seed=1), ("cpu", object()))
+
+
+@pytest.mark.parametrize("rows", [3, 70])
+def test_linear_with_bias_row_scale_and_gate(backend, rows):
+    """the product's options one by one against torch, on the weight-streaming kernel (few rows) and the tile kernel: a bias per
+    weight row, a scale per output row applied before it, the clamped gated unit, and the gated accumulate form"""
+    from leopard_b200 import _lib
+    eng = make_engine(model([attention_layer()]), O.random_weights(model([attention_layer()]), seed=1), backend)
+    dev = eng.device
+    g = torch.Generator().manual_seed(rows)
+    K, N = 20, 14
+    a = torch.randn(rows, K, generator=g)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    bias, scale = torch.randn(N, generator=g), torch.rand(rows, generator=g) + 0.5
+    gate, x0 = torch.randn(rows, N // 2, generator=g), torch.randn(rows, N // 2, generator=g)
+    z = (a.double() @ w.double().T) * scale.double()[:, None] + bias.double()
+    got = eng.linear(a.to(dev), w.to(dev), torch.float32, bias=bias.to(dev), row_scale=scale.to(dev))
+    assert rel_err(got, z) < TOL["float32"]
+    lim = 0.8
+    gg, uu = z[:, : N // 2].clamp(max=lim), z[:, N // 2:].clamp(-lim, lim)
+    unit = gg * torch.sigmoid(1.702 * gg) * (uu + 1)
+    got = eng.linear(a.to(dev), w.to(dev), torch.float32, _lib.EPI_CLAMP_GLU, lim, 1.702, bias=bias.to(dev), row_scale=scale.to(dev))
+    assert rel_err(got, unit) < TOL["float32"]
+    x = x0.clone().to(dev)
+    eng.linear(a.to(dev), w.to(dev), torch.float32, _lib.EPI_CLAMP_GLU, lim, 1.702, bias=bias.to(dev), row_scale=scale.to(dev),
+               into=(x, 0.3, gate.to(dev)))
+    assert rel_err(x, x0.double() + 0.3 * unit * torch.sigmoid(gate.double())) < TOL["float32"]
+
+
+@pytest.mark.parametrize("width", [12, 10])
+def test_elementwise_kernels(backend, width):
+    """Dynamic Tanh (one and two parameter sets, both operand precisions), the gated add, the depth average with its copy and the
+    gated RMS norm against torch, on widths that take the four-columns-a-thread path and the one-column path, on strided rows"""
+    from leopard_b200 import _lib
+    eng = make_engine(model([attention_layer()]), O.random_weights(model([attention_layer()]), seed=1), backend)
+    dev, L, st = eng.device, eng.L, eng._stream()
+    g = torch.Generator().manual_seed(width)
+    M = 5
+    wide = torch.randn(M, 3 * width + 4, generator=g).to(dev)
+    x = wide[:, width:2 * width]                                  # strided rows, base off the start
+    gain, shift = torch.randn(2, width, generator=g).to(dev), torch.randn(2, width, generator=g).to(dev)
+    for dtype in ("float32", "bfloat16"):
+        eng.act = torch.float32 if dtype == "float32" else torch.bfloat16
+        y1, y2 = eng.dyt(x * 3.0, (0.7, gain[0], shift[0]), (1.9, gain[1], shift[1]))
+        for y, al, k in ((y1, 0.7, 0), (y2, 1.9, 1)):
+            want = torch.tanh(al * 3.0 * x.double()) * gain[k].double() + shift[k].double()
+            assert rel_err(y.float(), want) < (TOL["float32"] if dtype == "float32" else 4e-3)
+    eng.act = torch.float32
+    acc0, y = torch.randn(M, width, generator=g).to(dev), wide[:, :width]
+    gt, yb, gb = wide[:, 2 * width:3 * width], shift[0], shift[1]
+    acc = acc0.clone()
+    eng._check(L.lp_gated_axpy_f32(_lib.ptr(acc), acc.stride(0), _lib.ptr(y), y.stride(0), _lib.ptr(yb), _lib.ptr(gt), gt.stride(0),
+                                   _lib.ptr(gb), 0.6, M, width, st), "lp_gated_axpy_f32")
+    assert rel_err(acc, acc0.double() + 0.6 * (y.double() + yb.double()) * torch.sigmoid(gt.double() + gb.double())) < TOL["float32"]
+    hist = torch.randn(4, M, width, generator=g).to(dev)
+    coef = torch.tensor([0.5, -1.25, 2.0], device=dev)
+    out, copy = torch.zeros(M, width, device=dev), hist[3]
+    eng._check(L.lp_depth_average_f32(_lib.ptr(hist), hist.stride(0), hist.stride(1), _lib.ptr(coef), 3, _lib.ptr(out), out.stride(0),
+                                      _lib.ptr(copy), copy.stride(0), M, width, st), "lp_depth_average_f32")
+    want = sum(float(coef[j]) * hist[j].double() for j in range(3))
+    assert rel_err(out, want) < TOL["float32"] and torch.equal(hist[3], out)
+    normed = torch.zeros(M, width, device=dev)
+    eng._check(L.lp_rmsnorm_gated_f32(_lib.ptr(x), x.stride(0), M, width, _lib.ptr(gain[0]), 1e-5, _lib.ptr(gt), gt.stride(0),
+                                      _lib.ptr(normed), normed.stride(0), 1, st), "lp_rmsnorm_gated_f32")
+    want = O.unit_rms(x.double(), 1e-5) * gain[0].double() * torch.sigmoid(gt.double())
+    assert rel_err(normed, want) < TOL["float32"]
