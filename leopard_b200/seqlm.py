@@ -1009,7 +1009,8 @@ class SeqLMEngine:
         h1 = self._empty((rows, f.expert_ff), self.act)
         y = self._empty((rows, D), F32)
         w_gu, w_dn = lw["w_gu"], lw["w_edown"]
-        if self.tensor_core_rows is not None and n_pairs >= f.experts * self.tensor_core_rows and h.dtype == BF16:
+        capturing = self.device.type == "cuda" and torch.cuda.is_current_stream_capturing()      # no host read inside a graph
+        if self.tensor_core_rows is not None and n_pairs >= f.experts * self.tensor_core_rows and h.dtype == BF16 and not capturing:
             # prefill in the serving precision: enough rows per expert to fill tensor-core tiles.  The segment bounds come to the host
             # (one small device -> host copy), the rows are gathered into expert order and every expert runs two tcgen05 GEMMs.
             groups = tile_group.cpu().tolist()
