@@ -128,6 +128,9 @@ def bench_kamosun(name, s, dev, steps, warmup, peaks, prompt):
     eng.L = TimedLib(plain)
     prefill()
     kp = eng.L.collect()
+    # the tcgen05 GEMM's launches by shape: which products the time goes to
+    out["prefill_gemm_shapes"] = [{"M": m, "N": n, "K": k, "ms": round(v[0], 4), "calls": v[1], "tflops": round(2.0 * m * n * k * v[1] / (v[0] * 1e-3) / 1e12, 1)}
+                                  for (m, n, k), v in sorted(eng.L.gemm_shapes.items(), key=lambda kv: -kv[1][0])]
     eng.L = plain
     hd = H * HEAD
     # the products that run on the tcgen05 GEMM: input projections (with the branch gates), output projections, dense and shared units

@@ -88,6 +88,7 @@ class TimedLib:
         self.ms = defaultdict(float)
         self.calls = defaultdict(int)
         self._pending = []
+        self.gemm_shapes = defaultdict(lambda: [0.0, 0])      # (M, N, K) of the tcgen05 GEMM -> [ms, calls] of the last collect()
 
     def __getattr__(self, name):
         fn = getattr(self._lib, name)
@@ -99,15 +100,20 @@ class TimedLib:
             e0.record()
             rc = fn(*a)
             e1.record()
-            self._pending.append((name, e0, e1))
+            shape = tuple(int(getattr(v, "value", v)) for v in a[6:9]) if name == "lp_gemm_bf16" else None
+            self._pending.append((name, e0, e1, shape))
             return rc
         return timed
 
     def collect(self):
         torch.cuda.synchronize()
-        for name, e0, e1 in self._pending:
+        self.gemm_shapes.clear()
+        for name, e0, e1, shape in self._pending:
             self.ms[name] += e0.elapsed_time(e1)
             self.calls[name] += 1
+            if shape is not None:
+                self.gemm_shapes[shape][0] += e0.elapsed_time(e1)
+                self.gemm_shapes[shape][1] += 1
         self._pending.clear()
         out = {k: {"ms": round(v, 4), "calls": self.calls[k]} for k, v in self.ms.items()}
         self.ms.clear()

@@ -64,31 +64,6 @@ rmsnorm_f32_kernel(const float* __restrict__ x, long long ldx, int M, int D, flo
   }
 }
 
-template <typename OT>
-__global__ void __launch_bounds__(NORM32_WARPS * 32)
-rmsnorm_gated_f32_kernel(const float* __restrict__ x, long long ldx, int M, int D, const float* __restrict__ gain, float eps,
-                         const float* __restrict__ gate, long long ldg, OT* __restrict__ out, long long ldo) {
-  const int row = blockIdx.x * NORM32_WARPS + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= M) return;
-  const float* xr = x + (long long)row * ldx;
-  float ss = 0.f;
-  for (int c = lane; c < D; c += 32) {
-    const float v = xr[c];
-    ss = fmaf(v, v, ss);
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  const float r = 1.0f / sqrtf(ss / (float)D + eps);
-  for (int c = lane; c < D; c += 32) {
-    float v = xr[c] * r;
-    if (gain != nullptr) v *= gain[c];
-    v /= 1.0f + expf(-gate[(long long)row * ldg + c]);
-    if constexpr (sizeof(OT) == 4) out[(long long)row * ldo + c] = v;
-    else out[(long long)row * ldo + c] = __float2bfloat16(v);
-  }
-}
-
 template <typename T> __device__ __forceinline__ float ld32(const T* p);
 template <> __device__ __forceinline__ float ld32<float>(const float* p) { return *p; }
 template <> __device__ __forceinline__ float ld32<bf16>(const bf16* p) { return __bfloat162float(*p); }
@@ -132,6 +107,37 @@ template <int V> __device__ __forceinline__ void stv(bf16* p, const f32vec<V>& x
     *reinterpret_cast<uint2*>(p) = u;
   } else {
     *p = __float2bfloat16(x.v[0]);
+  }
+}
+
+// a warp per row; the lanes take groups of V consecutive columns (V = 4: 16-byte reads of the row and of its gate)
+template <typename OT, int V>
+__global__ void __launch_bounds__(NORM32_WARPS * 32)
+rmsnorm_gated_f32_kernel(const float* __restrict__ x, long long ldx, int M, int D, const float* __restrict__ gain, float eps,
+                         const float* __restrict__ gate, long long ldg, OT* __restrict__ out, long long ldo) {
+  const int row = blockIdx.x * NORM32_WARPS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const float* xr = x + (long long)row * ldx;
+  float ss = 0.f;
+  for (int c = lane * V; c < D; c += 32 * V) {
+    const f32vec<V> v = ldv<V>(xr + c);
+#pragma unroll
+    for (int k = 0; k < V; ++k) ss = fmaf(v.v[k], v.v[k], ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float r = 1.0f / sqrtf(ss / (float)D + eps);
+  for (int c = lane * V; c < D; c += 32 * V) {
+    f32vec<V> v = ldv<V>(xr + c);
+    const f32vec<V> g = ldv<V>(gate + (long long)row * ldg + c);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      v.v[k] *= r;
+      if (gain != nullptr) v.v[k] *= gain[c + k];
+      v.v[k] /= 1.0f + expf(-g.v[k]);
+    }
+    stv<V>(out + (long long)row * ldo + c, v);
   }
 }
 
@@ -408,10 +414,15 @@ extern "C" int lp_rmsnorm_gated_f32(const float* x, long long ldx, int M, int D,
   LP_REQUIRE(x != nullptr && gate != nullptr && out != nullptr && M >= 0 && D > 0, "lp_rmsnorm_gated_f32: bad arguments");
   if (M == 0) return 0;
   const unsigned grid = (unsigned)((M + NORM32_WARPS - 1) / NORM32_WARPS);
-  if (out_fp32)
-    rmsnorm_gated_f32_kernel<float><<<grid, NORM32_WARPS * 32, 0, stream>>>(x, ldx, M, D, gain, eps, gate, ldg, reinterpret_cast<float*>(out), ldo);
+  const bool v4 = vec4_ok(D, {x, gate, out}, {ldx, ldg, ldo});
+  if (out_fp32 && v4)
+    rmsnorm_gated_f32_kernel<float, 4><<<grid, NORM32_WARPS * 32, 0, stream>>>(x, ldx, M, D, gain, eps, gate, ldg, reinterpret_cast<float*>(out), ldo);
+  else if (out_fp32)
+    rmsnorm_gated_f32_kernel<float, 1><<<grid, NORM32_WARPS * 32, 0, stream>>>(x, ldx, M, D, gain, eps, gate, ldg, reinterpret_cast<float*>(out), ldo);
+  else if (v4)
+    rmsnorm_gated_f32_kernel<bf16, 4><<<grid, NORM32_WARPS * 32, 0, stream>>>(x, ldx, M, D, gain, eps, gate, ldg, reinterpret_cast<bf16*>(out), ldo);
   else
-    rmsnorm_gated_f32_kernel<bf16><<<grid, NORM32_WARPS * 32, 0, stream>>>(x, ldx, M, D, gain, eps, gate, ldg, reinterpret_cast<bf16*>(out), ldo);
+    rmsnorm_gated_f32_kernel<bf16, 1><<<grid, NORM32_WARPS * 32, 0, stream>>>(x, ldx, M, D, gain, eps, gate, ldg, reinterpret_cast<bf16*>(out), ldo);
   note_launch();
   LP_CHECK_CUDA(cudaGetLastError());
   return 0;
